@@ -65,6 +65,10 @@ class LayerSpec:
     it joins the stream (``mixer_post_norm``, ``feed_forward_post_norm``):
     ``h += norm_b(mixer(norm(h))); h += norm_b(ffn(norm(h)))``.
 
+    With arrangement "parallel_gated" both sublayers read the same stream, each through its own norm, and each result
+    passes a learned gate: ``h += residual_scale * (sigmoid(W1 x1 + b1) * mixer(x1) + sigmoid(W2 x2 + b2) * ffn(x2))``,
+    ``x1 = norm1(h)``, ``x2 = norm2(h)`` (``mixer_gate_name``, ``feed_forward_gate_name``).
+
     ``weight_prefix`` is the checkpoint prefix of this layer ("model.layers.3.").
     ``cache_from`` is None when the layer owns its cache, or the index of the layer
     whose cache it reads (it then writes nothing): that of the latest run of that layer
@@ -87,6 +91,11 @@ class LayerSpec:
     feed_forward_post_norm: Optional[NormSpec] = None
     mixer_post_norm_name: str = "post_mixer_norm."
     feed_forward_post_norm_name: str = "post_feed_forward_norm."
+    # learned gates on the sublayers' results (arrangement "parallel_gated"): tensor names below weight_prefix of the
+    # matrices [hidden, hidden]; their biases are ``<name>.b``
+    mixer_gate_name: Optional[str] = None
+    feed_forward_gate_name: Optional[str] = None
+    residual_scale: float = 1.0                  # what a block adds to the stream is multiplied by it
 
 
 @dataclass(frozen=True)

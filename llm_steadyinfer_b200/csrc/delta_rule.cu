@@ -272,12 +272,13 @@ SI_EXPORT int si_delta_scan(const float* xc, long long xc_stride, const float* b
 }
 
 // ---- the read-out's norm and gate ------------------------------------------------------------------------------------
-//   out[t, h, :] = w * o[t, h, :] * rsqrt(mean(o[t, h, :]^2) + eps) * silu(z[t, h, :])      w [dv] shared by the heads
-// o fp32, z and out in the compute dtype (z a view with a row stride). One warp a (row, head).
+//   out[t, h, :] = post * w_h * o[t, h, :] * rsqrt(mean(o[t, h, :]^2) + eps) * silu(z[t, h, :])
+// w [dv] shared by the heads (w_head_stride 0) or [H, dv] with one row a head (w_head_stride dv); post one number.
+// o fp32, z and out in the compute dtype (z and out views with a row stride). One warp a (row, head).
 template <typename T>
 __global__ void __launch_bounds__(256) head_norm_gate_kernel(const float* __restrict__ o, long long o_stride, const T* __restrict__ z,
     long long z_stride, const float* __restrict__ w, T* __restrict__ out, long long out_stride, long long pairs, int H, int dv,
-    float eps) {
+    float eps, long long w_head_stride, float post) {
   pdl_prologue();
   const long long wi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wi >= pairs) return;
@@ -288,7 +289,8 @@ __global__ void __launch_bounds__(256) head_norm_gate_kernel(const float* __rest
   const T* zr = z + t * z_stride + (size_t)h * dv;
   float ss = 0.f;
   for (int i = lane; i < dv; i += 32) ss += orow[i] * orow[i];
-  const float rs = rsqrtf(warp_sum(ss) / (float)dv + eps);
+  const float rs = rsqrtf(warp_sum(ss) / (float)dv + eps) * post;
+  w += (size_t)h * w_head_stride;
   T* dst = out + t * out_stride + (size_t)h * dv;
   for (int i = lane; i < dv; i += 32) {
     const float zz = to_f32<T>(zr[i]);
@@ -298,16 +300,16 @@ __global__ void __launch_bounds__(256) head_norm_gate_kernel(const float* __rest
 
 SI_EXPORT int si_head_norm_gate(const float* o, long long o_stride, const void* z, int dtype, long long z_stride,
                                 const float* w, void* out, long long out_stride, int rows, int H, int dv, float eps,
-                                cudaStream_t stream) {
+                                long long w_head_stride, float post, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || dv <= 0) return -2;
   const long long pairs = (long long)rows * H;
   const dim3 grid((unsigned)((pairs + 7) / 8)), block(256);
   if (dtype == SI_BF16)
     si_launch(head_norm_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, o, o_stride, (const __nv_bfloat16*)z, z_stride, w,
-              (__nv_bfloat16*)out, out_stride, pairs, H, dv, eps);
+              (__nv_bfloat16*)out, out_stride, pairs, H, dv, eps, w_head_stride, post);
   else
     si_launch(head_norm_gate_kernel<float>, grid, block, 0, stream, o, o_stride, (const float*)z, z_stride, w, (float*)out,
-              out_stride, pairs, H, dv, eps);
+              out_stride, pairs, H, dv, eps, w_head_stride, post);
   return si_last_error();
 }

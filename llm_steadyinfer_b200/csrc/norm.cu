@@ -429,3 +429,37 @@ SI_EXPORT int si_add_norm_general(float* resid, const void* delta, const float* 
     return general_launch<float, __nv_bfloat16>(resid, delta, delta_bias, delta_weight, delta_eps, extra, vec, rows, weight, out, num_rows, hidden, eps, stream);
   return general_launch<float, float>(resid, delta, delta_bias, delta_weight, delta_eps, extra, vec, rows, weight, out, num_rows, hidden, eps, stream);
 }
+
+// ---- sublayer results through learned gates into the stream ---------------------------------------------------------------
+//   resid[t, :] += mult * (sigmoid(z1[t, :] + b1) * a[t, :] + sigmoid(z2[t, :] + b2) * f[t, :])
+// for blocks whose sublayers read the same stream side by side and are each gated, entry by entry, by a projection of
+// their own input (the second pair absent: one sublayer). z, a, f in the compute dtype, b fp32 [d], sums in fp32.
+template <typename T>
+__global__ void __launch_bounds__(256) gated_add_kernel(float* __restrict__ resid, const T* __restrict__ z1, const float* __restrict__ b1,
+    const T* __restrict__ a, const T* __restrict__ z2, const float* __restrict__ b2, const T* __restrict__ f, long long n, int d,
+    float mult) {
+  pdl_prologue();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(idx % d);
+    float s = to_f32<T>(a[idx]) / (1.f + expf(-(to_f32<T>(z1[idx]) + b1[c])));
+    if (z2) s += to_f32<T>(f[idx]) / (1.f + expf(-(to_f32<T>(z2[idx]) + b2[c])));
+    resid[idx] = fmaf(mult, s, resid[idx]);
+  }
+}
+
+SI_EXPORT int si_gated_add(float* resid, const void* z1, const float* b1, const void* a, const void* z2, const float* b2,
+                           const void* f, int dtype, int rows, int d, float mult, cudaStream_t stream) {
+  if (rows <= 0 || d <= 0) return 0;
+  if (!z1 || !b1 || !a || ((z2 != nullptr) != (f != nullptr)) || (z2 && !b2)) return -2;
+  const long long n = (long long)rows * d;
+  const int threads = 256;
+  const long long want = (n + threads - 1) / threads;
+  const int blocks = (int)(want < 8LL * si_sm_count() ? want : 8LL * si_sm_count());
+  if (dtype == SI_BF16)
+    si_launch(gated_add_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, resid, (const __nv_bfloat16*)z1, b1,
+              (const __nv_bfloat16*)a, (const __nv_bfloat16*)z2, b2, (const __nv_bfloat16*)f, n, d, mult);
+  else
+    si_launch(gated_add_kernel<float>, dim3(blocks), dim3(threads), 0, stream, resid, (const float*)z1, b1, (const float*)a,
+              (const float*)z2, b2, (const float*)f, n, d, mult);
+  return si_last_error();
+}

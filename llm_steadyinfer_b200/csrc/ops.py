@@ -1228,7 +1228,7 @@ def latent_expand_keys(plain, dense, keys, H: int, dq: int, dr: int, rk: int) ->
 
 def qk_prepare(rows, q_weight, k_weight, eps: float, inv_freq, rot_dims: int, interleaved: bool, positions, row_seq,
                block_table, k_cache, v_cache, page_size: int, num_seqs: int, NQ: int, NK: int, NV: int, dk: int, dv: int,
-               status=None, q_out=None, maps: int = 1) -> None:
+               status=None, q_out=None, maps: int = 1, whole: bool = False, rot_scale: float = 1.0) -> None:
     """Rows ``[q: NQ*dk | k: NK*dk | v: NV*dv | ...]`` of a stacked projection: every q and k vector is RMS-normalised
     (shared fp32 weights ``q_weight``, ``k_weight`` [dk]; None: no norm), its first ``rot_dims`` entries rotated by the
     row's position (pairs (2i, 2i+1) if ``interleaved``, else (i, i + rot_dims/2); angle pos * inv_freq[i]); q in place
@@ -1238,7 +1238,8 @@ def qk_prepare(rows, q_weight, k_weight, eps: float, inv_freq, rot_dims: int, in
     _cuda(rows, q_weight, k_weight, inv_freq, positions, row_seq, block_table, k_cache, v_cache, status)
     _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
     _need(rows.dim() == 2 and rows.stride(1) == 1 and rows.shape[1] >= (NQ + NK) * dk + NV * dv, "qk_prepare: row layout")
-    _f32v(q_weight, "q_weight", dk); _f32v(k_weight, "k_weight", dk)
+    _f32v(q_weight, "q_weight", NQ * dk if whole else dk); _f32v(k_weight, "k_weight", NK * dk if whole else dk)
+    _need(not whole or maps == 1, "qk_prepare: a norm over the whole projection goes without maps")
     _f32v(inv_freq, "inv_freq")
     _need(rot_dims == 0 or (inv_freq is not None and inv_freq.numel() >= rot_dims // 2), "qk_prepare: inv_freq too short")
     if q_out is None:
@@ -1257,11 +1258,12 @@ def qk_prepare(rows, q_weight, k_weight, eps: float, inv_freq, rot_dims: int, in
         num_pages = k_cache.shape[0]
     f = _fn("qk_prepare", "si_qk_prepare",
             [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_f, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_p])
+             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_p, _c_p])
     _check(f(_ptr(rows), _dt(rows), rows.stride(0), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), int(rot_dims),
              1 if interleaved else 0, _ptr(positions), _ptr(row_seq), _ptr(block_table),
              block_table.shape[1] if block_table is not None else 0, _ptr(k_cache), _ptr(v_cache), num_pages, page_size,
-             rows.shape[0], int(num_seqs), NQ, NK, NV, dk, dv, _ptr(q_out), q_out.stride(0), int(maps), _ptr(status), _stream()),
+             rows.shape[0], int(num_seqs), NQ, NK, NV, dk, dv, _ptr(q_out), q_out.stride(0), int(maps), 1 if whole else 0,
+             float(rot_scale), _ptr(status), _stream()),
            f"qk_prepare(dk={dk}, dv={dv})")
 
 
@@ -1279,6 +1281,101 @@ def diff_combine(a, gate, out, H: int, dv: int, ratio: int, lam: float, eps: flo
             [_c_p, _c_int, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_f, _c_f, _c_f, _c_p])
     _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), _dt(out),
              out.stride(0), T, H, dv, int(ratio), float(lam), float(eps), float(post), _stream()), f"diff_combine(heads={H}, dv={dv})")
+
+
+def talk_combine(a, talk, gate, out, H: int, G: int, dv: int, post: float = 1.0) -> None:
+    """Attention weights mixed over the heads, applied after the fact: ``a`` [T, H*G*dv] (fp32 or the compute dtype) holds
+    for every query head what its weights give on the values of each of the G key/value heads; out[t, h, :] =
+    post * sigmoid(gate[t, h, :]) * sum_g talk[h, g] * a[t, g, kv(h), :] with kv(h) = h // (H / G). ``talk`` fp32 [H, H],
+    ``gate`` [T, H*dv] in ``out``'s dtype (a strided view; None: no gate), ``out`` [T, H*dv] (a strided view)."""
+    _cuda(a, talk, gate, out)
+    T = a.shape[0]
+    _need(a.shape == (T, H * G * dv) and a.stride(1) == 1 and out.shape == (T, H * dv) and out.stride(1) == 1, "talk_combine: shapes")
+    _need(a.dtype in (out.dtype, torch.float32), "talk_combine: dtypes")
+    _f32v(talk, "talk", H * H)
+    if gate is not None:
+        _need(gate.shape == (T, H * dv) and gate.stride(1) == 1 and gate.dtype == out.dtype, "talk_combine: gate must be [T, H*dv]")
+    f = _fn("qk_prepare", "si_talk_combine",
+            [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_ll, _c_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(talk), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),
+             _dt(out), out.stride(0), T, H, G, dv, float(post), _stream()), f"talk_combine(heads={H}, dv={dv})")
+
+
+# ---- time mixing with a decaying matrix state ------------------------------------------------------------------------
+
+def shift_mix(x, mu, out, state, prev_off: int, positions, row_seq, q_start, slots, num_seqs: int, status=None) -> None:
+    """out[m, t, :] = x[t] + (x[t - 1] - x[t]) * mu[m] for every row t, where x[t - 1] is the row before in the same
+    sequence: the step's own, or for a portion's first row ``state[slot, prev_off:prev_off + d]`` (zeros at position 0),
+    which is then renewed with the portion's last row. ``x`` [T, d] (rows may have a stride), ``mu`` fp32 [M, d], ``out``
+    contiguous [M, T, d] in x's dtype, ``state`` fp32 [slots, n]."""
+    _cuda(x, mu, out, state, positions, row_seq, q_start, slots, status)
+    for t, nm in ((positions, "positions"), (row_seq, "row_seq"), (q_start, "q_start"), (slots, "slots")):
+        _i32(t, nm)
+    T, d = x.shape
+    M = mu.shape[0]
+    _need(x.stride(1) == 1 and out.shape == (M, T, d) and out.is_contiguous() and out.dtype == x.dtype, "shift_mix: out must be [M, T, d]")
+    _f32v(mu, "mu", M * d)
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and prev_off + d <= state.shape[1],
+          "shift_mix: state must be fp32 [slots, >= prev_off + d]")
+    f = _fn("time_mix", "si_shift_mix", [_c_p, _c_int, _c_ll, _c_p, _c_int, _c_p, _c_ll, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_p, _c_p,
+                                         _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(x), _dt(x), x.stride(0), _ptr(mu), M, _ptr(out), T * d, _ptr(state), state.stride(0), int(prev_off),
+             _ptr(positions), _ptr(row_seq), _ptr(q_start), _ptr(slots), T, int(num_seqs), d, _ptr(status), _stream()),
+           f"shift_mix(d={d})")
+
+
+def time_mix_prepare(r, k, v, z, w2t, w0, xs) -> None:
+    """``xs`` fp32 [T, 4C] = [r | k | v | decay] with decay = exp(-exp(tanh(z) @ w2t + w0)): ``r``, ``k``, ``v`` [T, C] and
+    ``z`` [T, L] in the compute dtype (views with a row stride), ``w2t`` fp32 [L, C], ``w0`` fp32 [C]."""
+    _cuda(r, k, v, z, w2t, w0, xs)
+    T, C = r.shape
+    L = z.shape[1]
+    _need(k.shape == (T, C) and v.shape == (T, C) and z.shape[0] == T and all(t.stride(1) == 1 for t in (r, k, v, z))
+          and r.dtype == k.dtype == v.dtype == z.dtype, "time_mix_prepare: r, k, v must be [T, C] and z [T, L] of one dtype")
+    _f32v(w2t, "w2t", L * C); _f32v(w0, "w0", C)
+    _need(xs.dtype == torch.float32 and xs.is_contiguous() and xs.shape == (T, 4 * C), "time_mix_prepare: xs must be fp32 [T, 4C]")
+    f = _fn("time_mix", "si_time_mix_prepare", [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_p, _c_p, _c_p,
+                                                _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(r), r.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(z), z.stride(0), _dt(r), _ptr(w2t), _ptr(w0),
+             _ptr(xs), T, C, L, _stream()), f"time_mix_prepare(C={C}, L={L})")
+
+
+def decay_state_floats(n: int) -> int:
+    """fp32 entries of one head's n x n state as ``decay_scan`` keeps it in a slot ([rows a thread][n][parts a column], the
+    rows padded to rows a thread x parts): the rule of ``decay_shape`` in time_mix.cu, restated so that a model's state size
+    is known without the library; ``decay_state_floats_of_library`` asks the library, and a test holds the two together."""
+    if n <= 0 or n > 512:
+        raise KernelError(f"decay_scan: a state of {n} x {n} is outside what the kernel supports")
+    r = (-(-n // 16) + 3) // 4 * 4
+    parts = 1
+    while parts * r < n:
+        parts *= 2
+    return r * parts * n
+
+
+def decay_state_floats_of_library(n: int) -> int:
+    lib = build.load("time_mix")
+    lib.si_decay_state_floats.restype = _c_ll
+    return lib.si_decay_state_floats(_c_int(n))
+
+
+def decay_scan(xs, u, state, y, q_start, ctx_len, slots, num_seqs: int, H: int, n: int) -> None:
+    """Per head o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(decay_t) S + k_t v_t^T, over every sequence's rows of
+    this step, from and into the first ``H * decay_state_floats(n)`` floats of ``state[slot]`` (fp32, in the kernel's own
+    order; from zero for a portion that starts at position 0). ``xs`` fp32 [T, 4*H*n] = [r | k | v | decay] as
+    ``time_mix_prepare`` leaves it, ``u`` fp32 [H, n], ``y`` fp32 [T, H*n]."""
+    _cuda(xs, u, state, y, q_start, ctx_len, slots)
+    for t, nm in ((q_start, "q_start"), (ctx_len, "ctx_len"), (slots, "slots")):
+        _i32(t, nm)
+    T = xs.shape[0]
+    _need(xs.dtype == torch.float32 and xs.stride(1) == 1 and xs.shape[1] == 4 * H * n, "decay_scan: xs must be fp32 [T, 4*H*n]")
+    _need(y.dtype == torch.float32 and y.shape == (T, H * n) and y.stride(1) == 1, "decay_scan: y must be fp32 [T, H*n]")
+    _f32v(u, "u", H * n)
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+          and state.shape[1] >= H * decay_state_floats(n), "decay_scan: state must be fp32 [slots, >= H * decay_state_floats(n)]")
+    f = _fn("time_mix", "si_decay_scan", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(xs), xs.stride(0), _ptr(u), _ptr(state), state.stride(0), _ptr(y), y.stride(0), _ptr(q_start), _ptr(ctx_len),
+             _ptr(slots), int(num_seqs), H, n, _stream()), f"decay_scan(heads={H}, n={n})")
 
 
 # ---- gated delta rule ------------------------------------------------------------------------------------------------
@@ -1342,18 +1439,21 @@ def delta_scan(xc, bg, state, y, q_start, ctx_len, slots, num_seqs: int, G: int,
              _ptr(ctx_len), _ptr(slots), int(num_seqs), G, H, dk, dv, _stream()), f"delta_scan(heads={H}, dk={dk}, dv={dv})")
 
 
-def head_norm_gate(o, z, weight, out, H: int, dv: int, eps: float) -> None:
-    """out[t, h, :] = weight * o[t, h, :] * rsqrt(mean(o[t, h, :]^2) + eps) * silu(z[t, h, :]); ``o`` fp32 [T, H*dv],
-    ``z`` and ``out`` [T, H*dv] in the compute dtype (views with a row stride are fine), ``weight`` fp32 [dv]."""
+def head_norm_gate(o, z, weight, out, H: int, dv: int, eps: float, post: float = 1.0) -> None:
+    """out[t, h, :] = post * weight * o[t, h, :] * rsqrt(mean(o[t, h, :]^2) + eps) * silu(z[t, h, :]); ``o`` fp32 [T, H*dv],
+    ``z`` and ``out`` [T, H*dv] in the compute dtype (views with a row stride are fine), ``weight`` fp32 [dv] (shared by
+    the heads) or [H*dv] (a row a head)."""
     _cuda(o, z, weight, out)
     T = o.shape[0]
     _need(o.dtype == torch.float32 and o.shape == (T, H * dv) and o.stride(1) == 1 and z.shape == (T, H * dv)
           and out.shape == (T, H * dv) and z.stride(1) == 1 and out.stride(1) == 1 and z.dtype == out.dtype,
           "head_norm_gate: shapes or dtypes")
-    _f32v(weight, "weight", dv)
-    f = _fn("delta_rule", "si_head_norm_gate", [_c_p, _c_ll, _c_p, _c_int, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_f, _c_p])
+    per_head = weight.numel() == H * dv and H > 1
+    _f32v(weight, "weight", H * dv if per_head else dv)
+    f = _fn("delta_rule", "si_head_norm_gate", [_c_p, _c_ll, _c_p, _c_int, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_f,
+                                                 _c_ll, _c_f, _c_p])
     _check(f(_ptr(o), o.stride(0), _ptr(z), _dt(z), z.stride(0), _ptr(weight), _ptr(out), out.stride(0), T, H, dv, float(eps),
-             _stream()), f"head_norm_gate(heads={H}, dv={dv})")
+             dv if per_head else 0, float(post), _stream()), f"head_norm_gate(heads={H}, dv={dv})")
 
 
 # ---- small elementwise steps -----------------------------------------------------------------------------------------
@@ -1386,3 +1486,108 @@ def glu_limited(gu, bias, out, group, limit: float, alpha: float) -> None:
     f = _fn("swiglu", "si_glu_limited", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_f, _c_p])
     _check(f(_ptr(gu), _ptr(bias), _ptr(out), _dt(out), T, F, F if group is None else int(group), float(limit), float(alpha),
              _stream()), f"glu_limited(F={F})")
+
+
+# ---- routed feed-forward (mixture of experts) ----------------------------------------------------------------------------
+
+MOE_ACTS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3}
+MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_route(x, w, E: int, top: int, scale: float, ids, wts, gates=None, scores: str = "sigmoid", renorm: bool = False) -> None:
+    """Scores of ``E`` experts for every row and the ``top`` largest: ``w`` [E + extra, d] holds the router's rows and
+    behind them ``extra`` gate rows; ``ids`` int32 [T, top], ``wts`` fp32 [T, top] = score * scale (``renorm``: divided by
+    the chosen scores' sum first), ``gates`` fp32 [T, extra] = sigmoid(w_gate . x). Scores are sigmoid(z) or softmax(z) of
+    z = w x, summed in fp32 whatever the storage."""
+    _cuda(x, w, ids, wts, gates)
+    T, d = x.shape
+    extra = w.shape[0] - E
+    _need(x.stride(1) == 1 and w.is_contiguous() and w.shape[1] == d and w.dtype == x.dtype and extra >= 0, "moe_route: x [T, d], w [E + extra, d]")
+    _need(scores in MOE_SCORES, f"moe_route: scores {scores!r} is not one of {sorted(MOE_SCORES)}")
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (T, top), "moe_route: ids must be int32 [T, top]")
+    _need(wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == (T, top), "moe_route: wts must be fp32 [T, top]")
+    if extra:
+        _need(gates is not None and gates.dtype == torch.float32 and gates.is_contiguous() and gates.shape == (T, extra),
+              "moe_route: gates must be fp32 [T, extra]")
+    f = _fn("moe", "si_moe_route", [_c_p, _c_int, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p,
+                                    _c_p, _c_int, _c_p])
+    _check(f(_ptr(x), _dt(x), x.stride(0), _ptr(w), E, extra, d, top, float(scale), MOE_SCORES[scores], 1 if renorm else 0,
+             _ptr(ids), _ptr(wts), _ptr(gates), T, _stream()), f"moe_route(experts={E}, top={top})")
+
+
+MOE_PLAN_CHUNK = 1024
+
+
+def moe_plan_ints(P: int, E: int) -> int:
+    """int32 entries of ``moe_plan``'s scratch for P pairs and E experts (ranks, then counts per chunk of 1,024 pairs)."""
+    return P + -(-P // MOE_PLAN_CHUNK) * E
+
+
+def moe_plan(ids, E: int, scratch, offsets, row_of, place_of) -> None:
+    """The (row, choice) pairs of ``ids`` [T, top] ordered by expert, rows in their own order within an expert:
+    ``offsets`` int32 [E + 1] (first place of every expert), ``row_of`` int32 [T*top] (the row at every place),
+    ``place_of`` int32 [T, top] (the place of every pair); ``scratch`` int32 [moe_plan_ints(T*top, E)]."""
+    _cuda(ids, scratch, offsets, row_of, place_of)
+    T, top = ids.shape
+    P = T * top
+    for t, nm in ((ids, "ids"), (scratch, "scratch"), (offsets, "offsets"), (row_of, "row_of"), (place_of, "place_of")):
+        _i32(t, nm)
+    _need(scratch.numel() >= moe_plan_ints(P, E) and offsets.numel() == E + 1 and row_of.numel() == P and place_of.numel() == P,
+          "moe_plan: sizes")
+    f = _fn("moe", "si_moe_plan", [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p])
+    _check(f(_ptr(ids), P, E, top, _ptr(scratch), _ptr(offsets), _ptr(row_of), _ptr(place_of), _stream()), f"moe_plan(experts={E})",
+           kernels=1 if P <= MOE_PLAN_CHUNK else 3)
+
+
+def moe_gemm(a, a_rows, w, out, offsets, act: str = "none") -> None:
+    """out[p, :] = act(a[row(p), :] @ w[e]^T) for every place p of expert e (``offsets`` int32 [E + 1] as ``moe_plan``
+    leaves them); row(p) = a_rows[p] (int32 [P]) or p itself (None). ``a`` [*, K] and ``w`` [E, N, K] of one dtype;
+    ``out`` [P, N] in that dtype or fp32. bf16 on the tensor cores with fp32 sums, fp32 in true 32-bit."""
+    _cuda(a, a_rows, w, out, offsets)
+    _i32(a_rows, "a_rows"); _i32(offsets, "offsets")
+    _need(act in MOE_ACTS, f"moe_gemm: act {act!r} is not one of {sorted(MOE_ACTS)}")
+    E, N, K = w.shape
+    P = out.shape[0]
+    _need(a.dim() == 2 and a.shape[1] == K and a.stride(1) == 1 and w.is_contiguous() and w.dtype == a.dtype, "moe_gemm: a [*, K], w [E, N, K]")
+    _need(out.shape == (P, N) and out.stride(1) == 1 and out.dtype in (a.dtype, torch.float32), "moe_gemm: out must be [P, N]")
+    _need(offsets.numel() == E + 1 and (a_rows is None or a_rows.numel() == P) and (a_rows is not None or a.shape[0] >= P), "moe_gemm: sizes")
+    f = _fn("moe", "si_moe_gemm", [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(a_rows), _ptr(w), _ptr(out), _dt(out), out.stride(0), _ptr(offsets), P, E, N, K,
+             MOE_ACTS[act], _stream()), f"moe_gemm(experts={E}, N={N}, K={K})")
+
+
+def moe_combine(y, place_of, wts, out, shared=None, gate=None) -> None:
+    """out[t, :] = sum_c wts[t, c] * y[place_of[t, c], :] (+ gate[t] * shared[t, :]): ``y`` [P, d] (fp32 or out's dtype),
+    ``place_of`` int32 [T, top], ``wts`` fp32 [T, top], ``shared`` [T, d] in out's dtype or None, ``gate`` fp32 [T] (a strided
+    view; None: 1), ``out`` [T, d]."""
+    _cuda(y, place_of, wts, out, shared, gate)
+    _i32(place_of, "place_of")
+    T, d = out.shape
+    top = wts.shape[1]
+    _need(y.shape[1] == d and y.stride(1) == 1 and out.stride(1) == 1 and y.dtype in (out.dtype, torch.float32), "moe_combine: y [P, d]")
+    _need(place_of.shape == (T, top) and wts.shape == (T, top) and wts.dtype == torch.float32 and wts.is_contiguous(), "moe_combine: wts, place_of")
+    if shared is not None:
+        _need(shared.shape == (T, d) and shared.stride(1) == 1 and shared.dtype == out.dtype, "moe_combine: shared must be [T, d]")
+    if gate is not None:
+        _need(shared is not None and gate.dtype == torch.float32 and gate.dim() == 1 and gate.shape[0] == T, "moe_combine: gate must be fp32 [T]")
+    f = _fn("moe", "si_moe_combine", [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_int, _c_p, _c_ll, _c_p, _c_int, _c_p, _c_int, _c_ll, _c_int, _c_int, _c_p])
+    _check(f(_ptr(y), _dt(y), y.stride(0), _ptr(place_of), _ptr(wts), top, _ptr(shared), shared.stride(0) if shared is not None else 0,
+             _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), _dt(out), out.stride(0), T, d, _stream()),
+           f"moe_combine(d={d})")
+
+
+# ---- gated sublayers into the stream ---------------------------------------------------------------------------------------
+
+def gated_add(resid, z1, b1, a, z2=None, b2=None, f=None, mult: float = 1.0) -> None:
+    """resid (fp32, in place) += mult * (sigmoid(z1 + b1) * a + sigmoid(z2 + b2) * f); the second sublayer may be absent.
+    ``z``, ``a``, ``f`` contiguous [T, d] of one dtype, ``b`` fp32 [d]."""
+    _cuda(resid, z1, b1, a, z2, b2, f)
+    T, d = resid.shape
+    _need(resid.dtype == torch.float32 and resid.is_contiguous(), "gated_add: resid must be contiguous fp32 rows")
+    for t in (z1, a, z2, f):
+        _need(t is None or (t.shape == (T, d) and t.is_contiguous() and t.dtype == z1.dtype), "gated_add: z, a, f must be [T, d] alike")
+    _need((z2 is None) == (f is None), "gated_add: the second sublayer needs its gate")
+    _f32v(b1, "b1", d); _f32v(b2, "b2", d)
+    fn = _fn("norm", "si_gated_add", [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(fn(_ptr(resid), _ptr(z1), _ptr(b1), _ptr(a), _ptr(z2), _ptr(b2), _ptr(f), _dt(z1), T, d, float(mult), _stream()),
+           f"gated_add(hidden={d})")

@@ -1,0 +1,304 @@
+// Time mixing with a decaying matrix state (the recurrence of RWKV-style mixers): per head a state S of n x n that
+// forgets by a decay per key channel and gains each token's outer product, read with a bonus for the current token:
+//   o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t;      S_t = diag(w_t) S_(t-1) + k_t v_t^T          S fp32, zero at the start
+// Three kernels.
+// `shift_mix`: the inputs of the mixer's products. Each product s reads x_t + (x_(t-1) - x_t) * mu_s, where x_(t-1) is
+// the row before in the same sequence: the step's own row, or for a portion's first row what the slot keeps from the
+// step before (zeros at position 0). The block of a portion's first row also renews the slot with the portion's last
+// row, so no two blocks touch a slot.
+// `time_mix_prepare`: decay = exp(-exp(W2 tanh(z) + w0)) per row and channel (z the low-rank product's first half, fp32
+// arithmetic throughout), written beside fp32 copies of r, k, v as rows [r | k | v | decay].
+// `decay_scan`: the recurrence. The columns of S are independent, so a block takes (sequence, head, a cut of the
+// columns); thread (column j, part p) keeps RPT neighbouring rows of column j in registers, the NP parts of a column are
+// neighbouring lanes whose partial read-outs are added with shuffles. r, k, decay and v of CHUNK tokens arrive by
+// cp.async in the half of shared memory that is not being computed on. A head's state lies in the slot as
+// [RPT][n][NP] (entry ((r * n + j) * NP + p) is row p * RPT + r of column j), so blocks read and write whole lines
+// whatever cut of the columns they have, and the cut changes no sum: the order of a row's sums depends on n alone.
+#include "common.cuh"
+#include <math.h>
+
+// ---- the shifted mixes ------------------------------------------------------------------------------------------------
+// x [T, d]; mu fp32 [M, d]; out [M][T, d] (matrix m at out + m * out_mat_stride); state fp32 [slots, state_stride] with
+// the previous row at prev_off.
+template <typename T>
+__global__ void __launch_bounds__(256) shift_mix_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ mu,
+    int M, T* __restrict__ out, long long out_mat_stride, float* __restrict__ state, long long state_stride, long long prev_off,
+    const int* __restrict__ positions, const int* __restrict__ row_seq, const int* __restrict__ q_start,
+    const int* __restrict__ slots, int num_seqs, int d, int* status) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  const int seq = row_seq[t];
+  if (seq < 0 || seq >= num_seqs) {                  // a padding row of a fixed-shape step: finite values, nothing kept
+    if (seq >= 0 && threadIdx.x == 0) set_status(status, SI_BAD_SEQ);
+    for (int m = 0; m < M; ++m)
+      for (int c = threadIdx.x; c < d; c += blockDim.x) out[(size_t)m * out_mat_stride + (size_t)t * d + c] = from_f32<T>(0.f);
+    return;
+  }
+  const int first_row = q_start[seq];
+  const bool first = t == first_row;
+  const int pos = positions[t];
+  const T* xr = x + (size_t)t * x_stride;
+  const T* xp = x + (size_t)(t - 1) * x_stride;
+  float* keep = state + (size_t)slots[seq] * state_stride + prev_off;
+  const T* xl = x + (size_t)(q_start[seq + 1] - 1) * x_stride;       // the portion's last row
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float h = to_f32<T>(xr[c]);
+    float prev;
+    if (!first) prev = to_f32<T>(xp[c]);
+    else {
+      prev = pos > 0 ? keep[c] : 0.f;
+      keep[c] = to_f32<T>(xl[c]);
+    }
+    const float diff = prev - h;
+    for (int m = 0; m < M; ++m)
+      out[(size_t)m * out_mat_stride + (size_t)t * d + c] = from_f32<T>(fmaf(diff, mu[(size_t)m * d + c], h));
+  }
+}
+
+SI_EXPORT int si_shift_mix(const void* x, int dtype, long long x_stride, const float* mu, int M, void* out,
+                           long long out_mat_stride, float* state, long long state_stride, long long prev_off,
+                           const int* positions, const int* row_seq, const int* q_start, const int* slots, int num_tokens,
+                           int num_seqs, int d, int* status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (M <= 0 || d <= 0 || prev_off < 0 || prev_off + d > state_stride) return -2;
+  const dim3 grid(num_tokens), block(d >= 1024 ? 256 : 128);
+  if (dtype == SI_BF16)
+    si_launch(shift_mix_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, x_stride, mu, M,
+              (__nv_bfloat16*)out, out_mat_stride, state, state_stride, prev_off, positions, row_seq, q_start, slots, num_seqs,
+              d, status);
+  else
+    si_launch(shift_mix_kernel<float>, grid, block, 0, stream, (const float*)x, x_stride, mu, M, (float*)out, out_mat_stride,
+              state, state_stride, prev_off, positions, row_seq, q_start, slots, num_seqs, d, status);
+  return si_last_error();
+}
+
+// ---- decay and fp32 copies ----------------------------------------------------------------------------------------------
+// r, k, v: rows of C values each in the compute dtype; z [T, L] likewise; w2t fp32 [L, C] (the second low-rank matrix,
+// transposed); w0 fp32 [C]; xs fp32 [T, 4C] = [r | k | v | decay]. A block takes PREP_ROWS rows, a thread a channel at a time.
+#define PREP_ROWS 4
+template <typename T>
+__global__ void __launch_bounds__(256) time_mix_prepare_kernel(const T* __restrict__ r, long long r_stride, const T* __restrict__ k,
+    long long k_stride, const T* __restrict__ v, long long v_stride, const T* __restrict__ z, long long z_stride,
+    const float* __restrict__ w2t, const float* __restrict__ w0, float* __restrict__ xs, int rows, int C, int L) {
+  extern __shared__ float th[];                      // [PREP_ROWS][L]: tanh of the rows' low-rank values
+  pdl_prologue();
+  const int t0 = blockIdx.x * PREP_ROWS;
+  for (int idx = threadIdx.x; idx < PREP_ROWS * L; idx += blockDim.x) {
+    const int rr = idx / L, l = idx - rr * L;
+    th[idx] = t0 + rr < rows ? tanhf(to_f32<T>(z[(size_t)(t0 + rr) * z_stride + l])) : 0.f;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc[PREP_ROWS];
+#pragma unroll
+    for (int rr = 0; rr < PREP_ROWS; ++rr) acc[rr] = 0.f;
+    for (int l = 0; l < L; ++l) {
+      const float w = w2t[(size_t)l * C + c];
+#pragma unroll
+      for (int rr = 0; rr < PREP_ROWS; ++rr) acc[rr] = fmaf(w, th[rr * L + l], acc[rr]);
+    }
+    const float b = w0[c];
+#pragma unroll
+    for (int rr = 0; rr < PREP_ROWS; ++rr) {
+      const int t = t0 + rr;
+      if (t >= rows) break;
+      float* o = xs + (size_t)t * 4 * C;
+      o[c] = to_f32<T>(r[(size_t)t * r_stride + c]);
+      o[C + c] = to_f32<T>(k[(size_t)t * k_stride + c]);
+      o[2 * C + c] = to_f32<T>(v[(size_t)t * v_stride + c]);
+      o[3 * C + c] = expf(-expf(acc[rr] + b));
+    }
+  }
+}
+
+SI_EXPORT int si_time_mix_prepare(const void* r, long long r_stride, const void* k, long long k_stride, const void* v,
+                                  long long v_stride, const void* z, long long z_stride, int dtype, const float* w2t,
+                                  const float* w0, float* xs, int rows, int C, int L, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (C <= 0 || L <= 0 || L > 2048) return -2;
+  const dim3 grid((rows + PREP_ROWS - 1) / PREP_ROWS), block(256);
+  const size_t smem = (size_t)PREP_ROWS * L * sizeof(float);
+  if (dtype == SI_BF16)
+    si_launch(time_mix_prepare_kernel<__nv_bfloat16>, grid, block, smem, stream, (const __nv_bfloat16*)r, r_stride,
+              (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, (const __nv_bfloat16*)z, z_stride, w2t, w0,
+              xs, rows, C, L);
+  else
+    si_launch(time_mix_prepare_kernel<float>, grid, block, smem, stream, (const float*)r, r_stride, (const float*)k, k_stride,
+              (const float*)v, v_stride, (const float*)z, z_stride, w2t, w0, xs, rows, C, L);
+  return si_last_error();
+}
+
+// ---- the recurrence -----------------------------------------------------------------------------------------------------
+#define DECAY_CHUNK 32
+
+__device__ __forceinline__ void tm_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void tm_cp16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+
+// Rows a thread (RPT, a multiple of 4) and parts a column (NP, a power of two up to 16, RPT * NP >= n).
+struct DecayShape { int rpt, np; };
+static DecayShape decay_shape(int n) {
+  DecayShape s;
+  s.rpt = ((n + 15) / 16 + 3) / 4 * 4;
+  int parts = 1;
+  while (parts * s.rpt < n) parts *= 2;
+  s.np = parts;
+  return s;
+}
+// fp32 entries of one head's state in a slot
+SI_EXPORT long long si_decay_state_floats(int n) {
+  if (n <= 0 || n > 512) return -1;
+  const DecayShape s = decay_shape(n);
+  return (long long)s.rpt * s.np * n;
+}
+
+// xs fp32 [T, 4C] = [r | k | v | decay], C = H * n; u fp32 [H, n]; y fp32 [T, C]. Shared memory: two buffers of CHUNK
+// tokens of [r: RPT * NP | k: RPT * NP | decay: RPT * NP | v: cols] (rows beyond n stay zero).
+template <int RPT, int NP>
+__global__ void __launch_bounds__(256) decay_scan_kernel(const float* __restrict__ xs, long long xs_stride,
+    const float* __restrict__ u, float* __restrict__ state, long long state_stride, float* __restrict__ y, long long y_stride,
+    const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ slots, int H, int n, int cols) {
+  extern __shared__ __align__(16) float sm[];
+  pdl_prologue();
+  const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * cols;
+  const int row0 = q_start[s], cnt = q_start[s + 1] - row0;
+  if (cnt <= 0) return;
+  const int pos0 = ctx_len[s] - cnt;
+  const int p = threadIdx.x % NP, jl = threadIdx.x / NP;
+  const int j = j0 + jl;
+  const bool col_ok = jl < cols && j < n;
+  const int C = H * n;
+  float* S = state + (size_t)slots[s] * state_stride + (size_t)h * RPT * NP * n + (size_t)(col_ok ? j : 0) * NP + p;
+  const size_t s_step = (size_t)n * NP;
+  float st[RPT], uu[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) {
+    st[r] = (col_ok && pos0 > 0) ? S[(size_t)r * s_step] : 0.f;
+    const int i = p * RPT + r;
+    uu[r] = i < n ? u[(size_t)h * n + i] : 0.f;
+  }
+  const int dkp = RPT * NP;
+  const int per_tok = 3 * dkp + ((cols + 3) & ~3);
+  for (int idx = threadIdx.x; idx < 2 * DECAY_CHUNK * per_tok; idx += blockDim.x) sm[idx] = 0.f;
+  __syncthreads();
+  const size_t head_off = (size_t)h * n;
+  const bool wide = n % 4 == 0 && xs_stride % 4 == 0 && ((uintptr_t)xs & 15) == 0;
+  const int unit = wide ? 4 : 1, per_part = n / unit, pieces = 3 * per_part;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  auto fetch = [&](int c0, int buf) {
+    const int cn = min(DECAY_CHUNK, cnt - c0);
+    for (int tt = warp; tt < cn; tt += nwarps) {
+      float* dst = sm + ((size_t)buf * DECAY_CHUNK + tt) * per_tok;
+      const float* row = xs + (size_t)(row0 + c0 + tt) * xs_stride + head_off;
+      for (int t = lane; t < pieces; t += 32) {
+        const int part = t / per_part, i = (t - part * per_part) * unit;      // 0 r, 1 k, 2 decay
+        const float* src = row + (size_t)(part == 2 ? 3 : part) * C + i;
+        if (wide) tm_cp16(dst + part * dkp + i, src);
+        else tm_cp4(dst + part * dkp + i, src);
+      }
+      for (int e = lane; e < cols; e += 32)
+        if (j0 + e < n) tm_cp4(dst + 3 * dkp + e, row + (size_t)2 * C + j0 + e);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  fetch(0, 0);
+  int buf = 0;
+  for (int c0 = 0; c0 < cnt; c0 += DECAY_CHUNK, buf ^= 1) {
+    const int cn = min(DECAY_CHUNK, cnt - c0);
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();                            // this chunk has arrived, and everyone is done with the other buffer
+    if (c0 + DECAY_CHUNK < cnt) fetch(c0 + DECAY_CHUNK, buf ^ 1);
+    const float* tok = sm + (size_t)buf * DECAY_CHUNK * per_tok;
+    float* yp = y + (size_t)(row0 + c0) * y_stride + head_off + j;
+#pragma unroll 2
+    for (int tt = 0; tt < cn; ++tt, tok += per_tok, yp += y_stride) {
+      const float4* r4 = reinterpret_cast<const float4*>(tok) + p * (RPT / 4);
+      const float4* k4 = reinterpret_cast<const float4*>(tok + dkp) + p * (RPT / 4);
+      const float4* w4 = reinterpret_cast<const float4*>(tok + 2 * dkp) + p * (RPT / 4);
+      const float vj = col_ok ? tok[3 * dkp + jl] : 0.f;
+      float rs = 0.f, bonus = 0.f;               // this thread's parts of r . S[:, j] and of sum_i r_i u_i k_i
+#pragma unroll
+      for (int c = 0; c < RPT / 4; ++c) {
+        const float4 rv = r4[c], kv = k4[c], wv = w4[c];
+        const float rr[4] = {rv.x, rv.y, rv.z, rv.w}, kk[4] = {kv.x, kv.y, kv.z, kv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = 4 * c + e;
+          rs = fmaf(rr[e], st[r], rs);
+          bonus = fmaf(rr[e] * uu[r], kk[e], bonus);
+          st[r] = fmaf(ww[e], st[r], kk[e] * vj);
+        }
+      }
+      float o = fmaf(bonus, vj, rs);
+#pragma unroll
+      for (int off = 1; off < NP; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (p == 0 && col_ok) *yp = o;
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) S[(size_t)r * s_step] = st[r];
+  }
+}
+
+SI_EXPORT int si_decay_scan(const float* xs, long long xs_stride, const float* u, float* state, long long state_stride,
+                            float* y, long long y_stride, const int* q_start, const int* ctx_len, const int* slots,
+                            int num_seqs, int H, int n, cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  if (H <= 0 || H > 65535 || n <= 0 || n > 512) return -2;
+  const DecayShape sh = decay_shape(n);
+  if (sh.rpt * sh.np < n || state_stride < (long long)H * sh.rpt * sh.np * n) return -2;
+  // columns a block: as many as 256 threads hold, fewer while the blocks do not fill the device (a block's tokens are a
+  // chain of dependent steps, so more blocks of fewer columns finish sooner); never less than a warp
+  int cols = 256 / sh.np;
+  if (cols > n) cols = n;
+  if (cols < 1) cols = 1;
+  const long long per = (long long)num_seqs * H;
+  while (cols > 1 && (cols / 2) * sh.np >= 32 && per * ((n + cols - 1) / cols) < si_sm_count()) cols /= 2;
+  const int zb = (n + cols - 1) / cols;
+  if (zb > 65535) return -2;
+  const int threads = ((cols * sh.np + 31) / 32) * 32;
+  const size_t smem = (size_t)2 * DECAY_CHUNK * (3 * sh.np * sh.rpt + ((cols + 3) & ~3)) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  const dim3 grid(num_seqs, H, zb), block(threads);
+#define DECAY_LAUNCH(R, P)                                                                                           \
+  {                                                                                                                  \
+    static size_t configured = 0;                                                                                    \
+    if (smem > 48 * 1024 && smem > configured) {                                                                     \
+      if (cudaFuncSetAttribute(decay_scan_kernel<R, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+        return -2;                                                                                                   \
+      configured = smem;                                                                                             \
+    }                                                                                                                \
+    si_launch(decay_scan_kernel<R, P>, grid, block, smem, stream, xs, xs_stride, u, state, state_stride, y, y_stride, \
+              q_start, ctx_len, slots, H, n, cols);                                                                  \
+  }
+  if (sh.np < 16) {
+    if (sh.rpt != 4) return -2;
+    switch (sh.np) {
+      case 1: DECAY_LAUNCH(4, 1) break;
+      case 2: DECAY_LAUNCH(4, 2) break;
+      case 4: DECAY_LAUNCH(4, 4) break;
+      case 8: DECAY_LAUNCH(4, 8) break;
+      default: return -2;
+    }
+  } else if (sh.np == 16) {
+    switch (sh.rpt) {                        // n up to 512: up to 32 rows a thread
+      case 4: DECAY_LAUNCH(4, 16) break;
+      case 8: DECAY_LAUNCH(8, 16) break;
+      case 12: DECAY_LAUNCH(12, 16) break;
+      case 16: DECAY_LAUNCH(16, 16) break;
+      case 20: DECAY_LAUNCH(20, 16) break;
+      case 24: DECAY_LAUNCH(24, 16) break;
+      case 28: DECAY_LAUNCH(28, 16) break;
+      case 32: DECAY_LAUNCH(32, 16) break;
+      default: return -2;
+    }
+  } else {
+    return -2;
+  }
+#undef DECAY_LAUNCH
+  return si_last_error();
+}

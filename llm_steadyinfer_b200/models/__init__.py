@@ -1,2 +1,2 @@
-from . import llama, mivorax, nufasun  # noqa: F401  (register "LlamaForCausalLM", "Mivorax", "Nufasun")
+from . import llama, mivorax, nufasun, vibunex  # noqa: F401  (register "LlamaForCausalLM", "Mivorax", "Nufasun", "Vibunex")
 from .model import Model

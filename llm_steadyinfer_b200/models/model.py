@@ -14,7 +14,7 @@ import torch
 
 from ..config.base import EmbedderSpec, ModelConfig, ModelSpec
 from ..csrc import ops
-from ..parts import Block, NormedDelta, embedder_class, feed_forward_class, mixer_class, norm_class, position_class
+from ..parts import Block, NormedDelta, SublayerGate, embedder_class, feed_forward_class, mixer_class, norm_class, position_class
 from ..parts.linear import configure_library_gemm, linear
 from ..engine import tracing
 
@@ -44,7 +44,12 @@ class Model:
                 n1b = norm_class(ls.mixer_post_norm.kind)(ls.mixer_post_norm.params, dtype, self.device)
             if ffn is not None and ls.feed_forward_post_norm is not None:
                 n2b = norm_class(ls.feed_forward_post_norm.kind)(ls.feed_forward_post_norm.params, dtype, self.device)
-            self.blocks.append(Block(mixer, ffn, n1, n2, ls.arrangement, n1b, n2b))
+            g1 = g2 = None                            # learned gates on the sublayers' results, where the layer has them
+            if ls.mixer_gate_name is not None:
+                g1 = SublayerGate({"size": self.spec.hidden_size}, dtype, self.device)
+            if ffn is not None and ls.feed_forward_gate_name is not None:
+                g2 = SublayerGate({"size": self.spec.hidden_size}, dtype, self.device)
+            self.blocks.append(Block(mixer, ffn, n1, n2, ls.arrangement, n1b, n2b, g1, g2, ls.residual_scale))
         self.final_norm = norm_class(self.spec.final_norm.kind)(self.spec.final_norm.params, dtype, self.device)
         # the embedder: by default the plain table under the spec's embedding name
         es = self.spec.embedder or EmbedderSpec("table", {})
@@ -75,6 +80,10 @@ class Model:
             yield p + ls.mixer_norm_name, b.mixer_norm
             if b.mixer_post_norm is not None:
                 yield p + ls.mixer_post_norm_name, b.mixer_post_norm
+            if b.mixer_gate is not None:
+                yield p + ls.mixer_gate_name, b.mixer_gate
+            if b.feed_forward_gate is not None:
+                yield p + ls.feed_forward_gate_name, b.feed_forward_gate
             if b.feed_forward is not None:
                 yield p + ls.feed_forward_prefix, b.feed_forward
                 yield p + ls.feed_forward_norm_name, b.feed_forward_norm

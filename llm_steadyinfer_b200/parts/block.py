@@ -13,8 +13,11 @@ The built-in "pre_norm" is the reference's block (src/source/model/llama3.cpp:99
     h += delta_in;  a = mixer(norm1(h));  h += norm1b(a);  f = ffn(norm2(h));  return norm2b(f), still to be added
 What it hands on is a ``NormedDelta``: the sublayer's raw result with the norm that belongs to it, which the next
 norm's launch normalises and adds before its own statistics (no launch of its own).
-Another arrangement (post-norm, parallel mixer and feed-forward, ...) is added with
-``register_arrangement`` and needs no change here.
+"parallel_gated" runs both sublayers on the same stream, each behind a norm of its own, and passes each result through
+a learned gate (``SublayerGate``: sigmoid of a projection of the sublayer's own input plus a bias, entry by entry):
+    h += delta_in;  x1 = norm1(h);  x2 = norm2(h);  h += scale * (gate1(x1) * mixer(x1) + gate2(x2) * ffn(x2))
+The add is one kernel in fp32 on the stream itself (``ops.gated_add``), so the block hands no pending delta on.
+Another arrangement (post-norm, ...) is added with ``register_arrangement`` and needs no change here.
 """
 from __future__ import annotations
 
@@ -22,7 +25,9 @@ from typing import Callable, Dict, Optional
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, NormedDelta
+from ..csrc import ops
+from .base import FeedForward, Mixer, Norm, NormedDelta, Part
+from .linear import linear
 
 _ARRANGEMENTS: Dict[str, Callable] = {}
 _CAPTURABLE: Dict[str, bool] = {}
@@ -43,16 +48,55 @@ def arrangement(name: str) -> Callable:
     return _ARRANGEMENTS[name]
 
 
+class SublayerGate(Part):
+    """A learned gate on a sublayer's result: ``sigmoid(W x + b)``, one number per coordinate, from the sublayer's own
+    input x. The part owns the matrix and the bias (tensor names: the part's prefix itself and ``.b``) and computes the
+    projection; the sigmoid and the product run in the kernel that adds the gated results into the stream."""
+    capturable = True
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        self.size = int(params["size"])
+        self.weight = self.bias = None
+
+    def weight_shapes(self):
+        return {"": (self.size, self.size), ".b": (self.size,)}
+
+    def keeps_dtype(self, name):
+        return name == ".b"
+
+    def norm_like(self, name):
+        return False
+
+    def load_weights(self, tensors):
+        self.weight = tensors[""].contiguous()
+        self.bias = tensors[".b"].float().contiguous()
+
+    def kernel_files(self, page_size):
+        return ("norm",) + (("gemm_f32",) if self.dtype == torch.float32 else ("gemm_skinny", "gemm_rows", "gemm_tc05"))
+
+    def project(self, x, ctx, key: str):
+        """``W x`` [T, size] in the compute dtype (the bias and the sigmoid belong to the adding kernel)."""
+        z = ctx.buf(key, (x.shape[0], self.size), self.dtype)
+        linear(x, self.weight, z, ctx.status)
+        return z
+
+
 class Block:
     def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Norm,
                  feed_forward_norm: Optional[Norm], arrangement_name: str = "pre_norm",
-                 mixer_post_norm: Optional[Norm] = None, feed_forward_post_norm: Optional[Norm] = None):
+                 mixer_post_norm: Optional[Norm] = None, feed_forward_post_norm: Optional[Norm] = None,
+                 mixer_gate: Optional[SublayerGate] = None, feed_forward_gate: Optional[SublayerGate] = None,
+                 residual_scale: float = 1.0):
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
         self.feed_forward_norm = feed_forward_norm
         self.mixer_post_norm = mixer_post_norm
         self.feed_forward_post_norm = feed_forward_post_norm
+        self.mixer_gate = mixer_gate
+        self.feed_forward_gate = feed_forward_gate
+        self.residual_scale = float(residual_scale)
         self.arrangement = arrangement_name
         self._run = arrangement(arrangement_name)
         self.capturable = _CAPTURABLE[arrangement_name]
@@ -108,3 +152,31 @@ def sandwich(block: Block, resid, delta, ctx, cache):
 
 
 register_arrangement("sandwich", sandwich, capturable=True)
+
+
+def parallel_gated(block: Block, resid, delta, ctx, cache):
+    if block.mixer_gate is None or (block.feed_forward is not None and block.feed_forward_gate is None):
+        raise ValueError("arrangement 'parallel_gated' needs a gate for each sublayer")
+    T, d = resid.shape
+    x1 = ctx.buf("block_x", (T, d), block.mixer.dtype)
+    block.norm(block.mixer_norm, resid, delta, x1, block.mixer.streams_first(T))
+    ff = block.feed_forward
+    x2 = None
+    if ff is not None:                                     # the same stream through the second norm (nothing left to add)
+        x2 = ctx.buf("block_x2", (T, d), block.mixer.dtype)
+        block.norm(block.feed_forward_norm, resid, None, x2)
+    a = block.mixer.forward(x1, ctx, cache)
+    z1 = block.mixer_gate.project(x1, ctx, "block_gate1")
+    if ff is None:
+        ops.gated_add(resid, z1, block.mixer_gate.bias, a, mult=block.residual_scale)
+        return None
+    f = ff.forward(x2, ctx)
+    if f.data_ptr() == a.data_ptr():
+        raise ValueError("arrangement 'parallel_gated': the mixer and the feed-forward return the same scratch buffer; "
+                         "the mixer's result must stay alive beside the feed-forward's")
+    z2 = block.feed_forward_gate.project(x2, ctx, "block_gate2")
+    ops.gated_add(resid, z1, block.mixer_gate.bias, a, z2, block.feed_forward_gate.bias, f, mult=block.residual_scale)
+    return None
+
+
+register_arrangement("parallel_gated", parallel_gated, capturable=True)

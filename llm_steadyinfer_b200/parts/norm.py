@@ -1,7 +1,8 @@
 """RMSNorm part: ``out = weight * h * rsqrt(mean(h^2) + eps)`` with ``h = resid + delta``
 written back to the fp32 residual stream. Formula of the reference's
 ``row_rmsnorm_f32_dim`` (src/source/op/kernels/cuda/rmsnorm_kernel.cu:8-60), whose eps is a
-constant in the kernel; here it is a parameter of the part.
+constant in the kernel; here it is a parameter of the part. With ``scalar`` the checkpoint holds one number
+for all coordinates (a tensor without dimensions), which is spread over the width when the weights are loaded.
 """
 from __future__ import annotations
 
@@ -22,16 +23,18 @@ class RMSNorm(Norm):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.name = params.get("weight_name", "weight")      # "" where the checkpoint names the vector by the prefix alone
+        self.scalar = bool(params.get("scalar", False))     # one number for all coordinates
         self.weight: Optional[torch.Tensor] = None
 
     def weight_shapes(self):
-        return {self.name: (self.size,)}
+        return {self.name: () if self.scalar else (self.size,)}
 
     def keeps_dtype(self, name: str) -> bool:
         return True
 
     def load_weights(self, tensors):
-        self.weight = tensors[self.name].contiguous()
+        w = tensors[self.name]
+        self.weight = (w.reshape(1).expand(self.size) if self.scalar else w).contiguous()
 
     def kernel_files(self, page_size):
         return ("norm",)

@@ -5,6 +5,11 @@ table entry j = 2i from ``theta^(-j/head_size)``). The reference has no frequenc
 the "llama3" rule rescales by wavelength ``lambda = 2*pi/f``:
 ``lambda < orig/high`` keeps f, ``lambda > orig/low`` gives ``f/factor``, and between them
 ``s = (orig/lambda - low)/(high - low)``, ``f' = (1 - s) * f/factor + s * f``.
+The "yarn" rule blends by the index of the pair instead: with ``edge(t) = rot_dim * ln(orig / (2 pi t)) / (2 ln theta)``,
+``lo = max(floor(edge(fast)), 0)``, ``hi = min(ceil(edge(slow)), rot_dim - 1)`` and
+``r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` it gives ``f' = f/factor * r_i + f * (1 - r_i)``, and the rotation's
+cosines and sines are multiplied by ``0.1 ln(factor) + 1`` (``Rotary.magnitude``, 1 for the other rules; mixers that
+support it pass it to the kernel that rotates).
 """
 from __future__ import annotations
 
@@ -19,7 +24,14 @@ def rotary_inverse_frequencies(rot_dim: int, theta: float, scaling) -> torch.Ten
     """fp32 [rot_dim/2], computed in float64 on the host."""
     i = torch.arange(0, rot_dim, 2, dtype=torch.float64)
     f = 1.0 / (float(theta) ** (i / rot_dim))
-    if scaling is not None:
+    if scaling is not None and scaling.get("rope_type") == "yarn":
+        factor, orig = float(scaling["factor"]), float(scaling["original"])
+        edge = lambda t: rot_dim * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(float(theta)))
+        lo = max(math.floor(edge(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(edge(float(scaling["slow"]))), rot_dim - 1)
+        ramp = torch.clamp((i / 2 - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        f = f / factor * ramp + f * (1.0 - ramp)
+    elif scaling is not None:
         kind = scaling.get("rope_type")
         if kind != "llama3":
             raise ValueError(f"rotary: scaling rule {kind!r} is not supported")
@@ -43,8 +55,10 @@ class Rotary(PositionEncoding):
         self.rot_dim = int(params.get("rot_dim") or self.head_dim)
         if self.rot_dim % 2 or self.rot_dim > self.head_dim:
             raise ValueError(f"rotary: rot_dim {self.rot_dim} must be even and at most head_dim")
-        self.inv_freq = rotary_inverse_frequencies(
-            self.rot_dim, params["theta"], params.get("scaling")).to(device)
+        scaling = params.get("scaling")
+        self.inv_freq = rotary_inverse_frequencies(self.rot_dim, params["theta"], scaling).to(device)
+        # what the rotation's cosines and sines are multiplied by (the yarn rule; mixers whose kernels take it ask for it)
+        self.magnitude = 0.1 * math.log(float(scaling["factor"])) + 1.0 if scaling and scaling.get("rope_type") == "yarn" else 1.0
 
     def rotary(self):
         return self.inv_freq, self.rot_dim
