@@ -105,5 +105,5 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata=None
         f.write(blob)
         for name in order:
             t = tensors[name].detach().cpu().contiguous()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")   # reshape: a tensor of no dimensions too
     os.replace(tmp, path)

@@ -180,10 +180,21 @@ def routed_feed_forward(h, w, p, mlp):
     return out
 
 
+def routing_margin(h, w, p, mlp):
+    """Per row, the gap between the smallest chosen score and the largest one left out (inf when all are chosen): a
+    row whose gap is tiny may choose otherwise when h is rounded, which is no fault."""
+    E, top = mlp["router"]["experts"], mlp["router"]["top"]
+    if top >= E:
+        return torch.full((h.shape[0],), math.inf, dtype=F64)
+    s = sigmoid(h @ w[p + "router"].t()).sort(-1, descending=True).values
+    return s[:, top - 1] - s[:, top]
+
+
 # ---- the model ------------------------------------------------------------------------------
 
-def forward(cfg, w, tokens, return_layers=False):
-    """Logits [T, vocab] of one whole sequence (and the residual stream after every layer).
+def forward(cfg, w, tokens, return_layers=False, margins=None):
+    """Logits [T, vocab] of one whole sequence (and the residual stream after every layer; ``margins``, a list, gains
+    every routed layer's ``routing_margin``).
     A layer: x <- x + m (sigmoid(W_rg1 h1 + b1) * mixer(h1) + sigmoid(W_rg2 h2 + b2) * ff(h2)), h1 = norm1(x),
     h2 = norm2(x), norm(x) = x / sqrt(mean(x^2) + eps) * g with one number g."""
     eps = cfg["norm"]["eps"]
@@ -203,6 +214,8 @@ def forward(cfg, w, tokens, return_layers=False):
         if layer.get("mlp") is not None:
             h2 = rms(x, eps) * w[p + "norm2"]
             ff = routed_feed_forward(h2, w, p + "mlp.", layer["mlp"])
+            if margins is not None:
+                margins.append(routing_margin(h2, w, p + "mlp.", layer["mlp"]))
             delta = delta + ff * sigmoid(h2 @ w[p + "rg2"].t() + w[p + "rg2.b"])
         x = x + m * delta
         layers.append(x.clone())

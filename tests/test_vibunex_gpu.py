@@ -1,0 +1,586 @@
+"""Vibunex on the GPU against the plain implementation (tests/plain_vibunex.py): every mechanism alone, prompts against
+token-by-token decoding, portions down to two tokens, unequal batches with pages and slots used again, keys far away
+and at page borders, the first tokens, long decoding, other sizes, and greedy generation through the entry point.
+Weights come from tests/vibunex_configs.py, which makes them so that a lost key, sink, state or expert shows."""
+import json
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_vibunex as pv
+import replay_util as ru
+import vibunex_configs as vc
+
+pytestmark = pytest.mark.gpu
+
+# A row's error: root mean square of the difference of the logits (mean taken off) over that of the plain logits.
+# In 32-bit every row is held to the limit. In bfloat16 rounding alone gives a median well below the limit with single
+# rows above it: the limit holds for the median and for all but one row in twenty, and no row may pass four times the
+# limit. A row whose router had two scores closer than MARGIN at the edge of its choice may choose otherwise in
+# bfloat16, which is no fault: such rows are left out there. What a cut, a batch or a page does wrong shows in 32-bit.
+LIMIT = {torch.float32: 2e-4, torch.bfloat16: 8e-2}
+MARGIN = 0.03
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["fp32", "bf16"]
+DEV = "cuda:0"
+
+
+class Plain(ru.PlainLogits):
+    """The plain logits of a request and, per position, the smallest routing margin of any layer."""
+
+    def __init__(self, folder):
+        super().__init__(folder, pv)
+        self._margins = {}
+
+    def of(self, tokens):
+        key = tuple(tokens)
+        if key not in self._cache:
+            m = []
+            self._cache[key] = pv.forward(self.cfg, self.w, tokens, margins=m)
+            self._margins[key] = torch.stack(m).min(0).values if m else torch.full((len(key),), math.inf, dtype=torch.float64)
+        return self._cache[key]
+
+    def margin(self, tokens, p):
+        self.of(tokens)
+        return self._margins[tuple(tokens)][p].item()
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("vibunex")
+    return {n: vc.write_folder(os.path.join(str(root), n), cfg, seed=31 + i) for i, (n, cfg) in enumerate(vc.CONFIGS.items())}
+
+
+@pytest.fixture(scope="module")
+def plains(folders):
+    return {n: Plain(d) for n, d in folders.items()}
+
+
+def replayer(folder, name, dtype, max_tokens, max_requests=4):
+    from llm_steadyinfer_b200.engine.replay import Replayer
+    return Replayer(folder, dtype, max_tokens, page_size=vc.PAGE_SIZE[name], max_requests=max_requests)
+
+
+def row_error(row, ref):
+    d = row.to(torch.float64) - ref
+    d = d - d.mean()
+    return (d.pow(2).mean().sqrt() / ref.sub(ref.mean()).pow(2).mean().sqrt()).item()
+
+
+def check(rp, steps, reqs, plain, dtype, what):
+    worst, n, errors = 0.0, 0, []
+    hard = LIMIT[dtype] * (4 if dtype == torch.bfloat16 else 1)
+    for rid, p, row in ru.replay_in_process(rp, steps):
+        assert torch.isfinite(row).all(), f"{what}: request {rid!r} position {p}: logits are not finite"
+        if dtype == torch.bfloat16 and plain.margin(reqs[rid], p) < MARGIN:
+            continue
+        e = row_error(row, plain.of(reqs[rid])[p])
+        assert e == e and e <= hard, f"{what}: request {rid!r} position {p}: error {e:.3e} (allowed {hard:.0e})"
+        worst, n = max(worst, e), n + 1
+        errors.append(e)
+    assert n > 0
+    if dtype == torch.bfloat16:
+        errors.sort()
+        over = sum(e > LIMIT[dtype] for e in errors)
+        assert over <= max(1, n // 20), f"{what}: {over} of {n} rows above {LIMIT[dtype]:.0e}"
+        assert errors[n // 2] <= LIMIT[dtype] / 2 or n < 4, f"{what}: median error {errors[n // 2]:.3e}"
+    mgr = rp.runner.manager
+    mgr.check_invariant()
+    assert not mgr.requests
+    assert all(mgr.free_pages(g) == mgr.groups[g].pool.num_pages for g in range(len(mgr.groups)))
+    return worst
+
+
+def requests_of(name, lengths, seed=0):
+    vocab = vc.CONFIGS[name]["vocab"]
+    return {f"q{i}": ru.random_tokens(vocab, n, 1000 * seed + i) for i, n in enumerate(lengths)}
+
+
+# ---- each mechanism alone, and the layers of a whole model one by one ------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("name", ["left", "right", "mlp"])
+def test_each_mechanism_alone(folders, plains, name, dtype):
+    """One-layer models in which one mixer's scale is zero (or both nearly, for the feed-forward): the logits whole and
+    token by token."""
+    reqs = requests_of(name, [1, 2, 37, 90])
+    for mode, steps in (("whole", ru.trace_whole(reqs)), ("tail", ru.trace_tail(reqs, tail=30))):
+        rp = replayer(folders[name], name, dtype, 128)
+        check(rp, steps, reqs, plains[name], dtype, f"{name}/{mode}")
+
+
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
+def test_layers_one_by_one_in_32_bit(folders, name):
+    """The residual stream after every layer against the plain one."""
+    toks = ru.random_tokens(vc.CONFIGS[name]["vocab"], 45, 5)
+    cfg, w = pv.read_model_folder(folders[name])
+    _, want = pv.forward(cfg, w, toks, return_layers=True)
+    rp = replayer(folders[name], name, torch.float32, 64)
+    got = {}
+    rp.runner.model.hook_layers(lambda run, resid: got.__setitem__(run, resid.double().cpu()))
+    rp.run_step([{"id": "a", "tokens": toks, "want": [len(toks) - 1]}], end=["a"])
+    assert sorted(got) == list(range(len(cfg["layers"])))
+    for run in range(len(cfg["layers"])):
+        scale = want[run].abs().max().item()
+        diff = (got[run] - want[run]).abs().max().item()
+        assert diff <= 5e-5 * scale, f"{name}: layer {run} differs by {diff:.2e} of {scale:.1f}"
+
+
+# ---- schedules ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_schedules(folders, plains, name, dtype, mode):
+    reqs = requests_of(name, [1, 3, 19, 64, 65, 130, 201], seed=1)
+    longest = ru.round64(max(len(t) for t in reqs.values()))
+    if mode == "whole":
+        steps, max_tokens = ru.trace_whole(reqs), longest
+    elif mode == "tail":
+        steps, max_tokens = ru.trace_tail(reqs, tail=40), longest
+    elif mode == "portions":
+        steps, max_tokens = ru.trace_portions(reqs, sizes=(2, 17, 3, 2, 31, 5, 64, 2, 9, 1, 40)), longest
+    else:
+        max_tokens = longest + 128                       # two or three live at a time: pages and slots come again
+        steps = ru.trace_mixed(reqs, max_tokens, seed=3, max_live=3)
+    rp = replayer(folders[name], name, dtype, max_tokens, max_requests=3)
+    worst = check(rp, steps, reqs, plains[name], dtype, f"{name}/{mode}")
+    print(f"{name} {mode} {dtype}: worst row error {worst:.2e}")
+
+
+def test_batch_equals_alone_and_slots_come_again(folders, plains):
+    """Unequal requests in one batch against each alone, with two state slots for five requests: every slot and page is
+    used again, and what the request before left there (matrix state, the last row, keys) must not show."""
+    name, dtype = "mixed_a", torch.float32
+    reqs = requests_of(name, [70, 9, 33, 2, 51], seed=2)
+    steps = ru.trace_mixed(reqs, 192, seed=9, max_live=2, prompt_frac=0.5)
+    rp = replayer(folders[name], name, dtype, 192, max_requests=2)
+    check(rp, steps, reqs, plains[name], dtype, "two slots")
+    again = dict(reversed(list(reqs.items())))
+    check(rp, ru.trace_mixed(again, 192, seed=10, max_live=2, prompt_frac=0.3), again, plains[name], dtype, "two slots again")
+
+
+def test_long_decoding(folders, plains):
+    """A short prompt, then 300 tokens one by one, across many page borders; the matrix state and the last row are
+    carried 300 times."""
+    name = "mixed_a"
+    reqs = requests_of(name, [310], seed=3)
+    for dtype in DTYPES:
+        rp = replayer(folders[name], name, dtype, 320)
+        check(rp, ru.trace_tail(reqs, tail=300), reqs, plains[name], dtype, "long decoding")
+
+
+def test_first_tokens(folders, plains):
+    """Positions 0, 1, 2 alone and as the start of portions: zeros as the row before the first, a state that starts at
+    zero (the bonus alone answers), a softmax over one key and the sink, a rotation by angle zero."""
+    name = "mixed_b"
+    reqs = requests_of(name, [1, 2, 3, 5], seed=4)
+    for dtype in DTYPES:
+        for sizes in ((1,), (2, 1), (1, 2)):
+            rp = replayer(folders[name], name, dtype, 64)
+            check(rp, ru.trace_portions(reqs, sizes=sizes), reqs, plains[name], dtype, f"first tokens {sizes}")
+
+
+def test_a_token_far_back_reaches_through_the_state(tmp_path):
+    """Time mixing whose decay is almost one, attention switched off: what token 3 wrote into the matrix state is read
+    400 tokens later. The logits with another token at place 3 must differ in the plain implementation, and the engine
+    must follow it, cut in portions."""
+    cfg = vc._model(120, 64, 1e-5, [vc._layer(vc._left(2, 1, 8, 8, 8), (4, 16), None, left_scale=0.0, right_scale=1.0, rank=4)])
+
+    def slow_decay(t):
+        t["l0.mix.right.w0"][:] = -9.0                    # decay about exp(-1e-4) a token
+        t["l0.mix.right.w2"][:] = 0.0
+
+    folder = vc.write_folder(str(tmp_path / "far"), cfg, 5, change=slow_decay)
+    plain = Plain(folder)
+    a = ru.random_tokens(120, 420, 77)
+    b = list(a)
+    b[3] = (a[3] + 17) % 120
+    assert row_error(plain.of(a)[-1], plain.of(b)[-1]) > 20 * LIMIT[torch.float32], "the test's weights do not carry the far token"
+    for dtype in DTYPES:
+        rp = replayer(folder, "right", dtype, 448)
+        reqs = {"a": a, "b": b}
+        check(rp, ru.trace_portions(reqs, sizes=(64, 2, 100, 31, 1)), reqs, plain, dtype, "far token")
+
+
+def test_a_key_far_back_and_the_sink_reach_through_attention(tmp_path):
+    """Attention alone, with norm weights that make scores large: a token repeated far back holds most of a late row's
+    weight, so changing the token there changes the logits; and so does the sink (its learned number raised to the size
+    of the largest scores)."""
+    cfg = vc._model(120, 64, 1e-5, [vc._layer(vc._left(4, 2, 16, 8, 8, scale=0.5), (2, 8), None, left_scale=1.0, right_scale=0.0, rank=4)])
+
+    def sharp(t):
+        t["l0.mix.left.q.norm"] *= 1.6
+        t["l0.mix.left.k.norm"] *= 1.6
+
+    def sharp_other_sink(t):
+        sharp(t)
+        t["l0.mix.left.sink"] += 15.0
+
+    folder = vc.write_folder(str(tmp_path / "key"), cfg, 6, change=sharp)
+    other = vc.write_folder(str(tmp_path / "sink"), cfg, 6, change=sharp_other_sink)
+    plain, plain_sink = Plain(folder), Plain(other)
+    a = ru.random_tokens(120, 400, 78)
+    b = list(a)
+    b[5] = (a[5] + 31) % 120
+    rows = range(300, 400)
+    assert max(row_error(plain.of(a)[i], plain.of(b)[i]) for i in rows) > 20 * LIMIT[torch.float32], "no late row looks at place 5"
+    assert row_error(plain.of(a)[-1], plain_sink.of(a)[-1]) > 20 * LIMIT[torch.float32], "the sink does not count"
+    for dtype in DTYPES:
+        reqs = {"a": a, "b": b}
+        check(replayer(folder, "left", dtype, 448), ru.trace_portions(reqs, sizes=(290, 2, 50, 1, 1, 17)), reqs, plain, dtype, "far key")
+        check(replayer(other, "left", dtype, 448), ru.trace_tail({"a": a}, tail=20), {"a": a}, plain_sink, dtype, "another sink")
+
+
+# ---- kernels with inputs that make one key count -----------------------------------------------------------
+
+def _paged(rows, page_size, perm_seed):
+    """rows [n, heads, d] into a shuffled page pool; returns (cache [pages, heads, page_size, d], table [1, blocks])."""
+    n, KV, d = rows.shape
+    blocks = -(-n // page_size)
+    g = torch.Generator().manual_seed(perm_seed)
+    pages = torch.randperm(blocks + 3, generator=g)[:blocks]
+    cache = torch.zeros(blocks + 3, KV, page_size, d, dtype=rows.dtype)
+    for j in range(n):
+        cache[pages[j // page_size], :, j % page_size] = rows[j]
+    return cache, pages.to(torch.int32).view(1, -1)
+
+
+def _mixed_heads(q, k, v, scale, sink, talk, window=None):
+    """Plain: per head the sink-softmax weights (a window, where given, masks keys further back than window - 1),
+    mixed over the heads, applied to the values of the head's own key/value head. q [n, H, dk], k [n, G, dk], v [n, G, dv]."""
+    n, H, _ = q.shape
+    G = k.shape[1]
+    ratio = H // G
+    ws = []
+    for h in range(H):
+        if window is None:
+            ws.append(pv.sink_softmax_weights(q[:, h], k[:, h // ratio], scale, sink[h]))
+        else:
+            s = (q[:, h] @ k[:, h // ratio].t()) * scale
+            i, j = torch.arange(n)[:, None], torch.arange(n)[None, :]
+            s = s.masked_fill((j > i) | (j < i - window + 1), -math.inf)
+            m = torch.maximum(s.max(-1, keepdim=True).values, sink[h])
+            e = torch.exp(s - m)
+            ws.append(e / (e.sum(-1, keepdim=True) + torch.exp(sink[h] - m)))
+    mixed = torch.einsum("hg,gij->hij", talk, torch.stack(ws))
+    return torch.stack([mixed[h] @ v[:, h // ratio] for h in range(H)], 1)          # [n, H, dv]
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("H,G,dk,dv,window", [(4, 2, 24, 40, None), (6, 3, 16, 8, 37), (8, 2, 64, 32, None), (3, 1, 10, 6, 64), (5, 5, 32, 16, None)])
+def test_mixed_attention_far_keys_page_borders_and_the_sink(H, G, dk, dv, window, dtype):
+    """Queries built so that one key carries nearly all of a head's weight: keys at page borders, a key far back, and (the
+    part offers a window, though this design does not use one) the key just inside and the one just outside it. The values
+    of a token lie side by side as one value head; every query head runs over it and the mix picks its own. Rows run as a
+    prompt and once more one by one; the tensor-core kernel too where the sizes allow it."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(3 + H)
+    n, ps = 330, 16
+    ratio = H // G
+    k = torch.randn(n, G, dk) * 0.3
+    v = torch.randn(n, G, dv)
+    q = torch.randn(n, H, dk) * 0.3
+    w = window or n
+    dists = sorted({0, 1, w - 2, w - 1, w, w + 1, 15, 16, 17, 31, 32, 33, 250, 300} & set(range(n)))
+    for e, dist in enumerate(dists):                      # query i looks hard at the key `dist` back
+        i = n - 1 - e
+        if i - dist < 0:
+            continue
+        k[i - dist] = k[i - dist] / k[i - dist].norm(dim=-1, keepdim=True) * 6.0
+        for h in range(H):
+            q[i, h] = k[i - dist, h // ratio] * (1.5 if h % 2 else 1.0)
+    q, k, v = (t.to(dtype).float() for t in (q, k, v))
+    scale = 0.5
+    sink = torch.linspace(-1.0, 12.0, H, dtype=torch.float64)           # from nothing to the size of the largest score
+    talk = torch.eye(H, dtype=torch.float64) * 0.7 + 0.4 * torch.randn(H, H, dtype=torch.float64)
+    gate = torch.randn(n, H * dv).to(dtype)
+    want = _mixed_heads(q.double(), k.double(), v.double(), scale, sink, talk, window).reshape(n, H * dv)
+    want = want * torch.sigmoid(gate.double()) * 0.8
+    if window:                                            # the key just outside would have dominated
+        i = n - 1 - dists.index(window)
+        wider = _mixed_heads(q.double(), k.double(), v.double(), scale, sink, talk, window + 1).reshape(n, H * dv)
+        assert (wider[i] - _mixed_heads(q.double(), k.double(), v.double(), scale, sink, talk, window).reshape(n, H * dv)[i]).abs().max() > 0.1
+    no_sink = _mixed_heads(q.double(), k.double(), v.double(), scale, sink - 50.0, talk, window).reshape(n, H * dv)
+    assert (no_sink * torch.sigmoid(gate.double()) * 0.8 - want).abs().max() > 0.05, "the sink does not count in this test"
+    qd = q.reshape(n, H * dk).to(dtype).to(DEV)
+    kc, table = _paged(k.to(dtype), ps, 3)
+    vc_, _ = _paged(v.reshape(n, 1, G * dv).to(dtype), ps, 3)
+    kc, vc_, table = kc.to(DEV), vc_.to(DEV), table.to(DEV)
+    seqs, pos = torch.zeros(n, dtype=torch.int32, device=DEV), torch.arange(n, dtype=torch.int32, device=DEV)
+    sink_d, talk_d, gate_d = sink.float().to(DEV), talk.float().to(DEV).contiguous(), gate.to(DEV)
+    limit = 1e-4 if dtype == torch.float32 else 3e-2
+
+    def finish(a, rows=slice(None)):
+        out = torch.zeros(a.shape[0], H * dv + 8, dtype=dtype, device=DEV)      # a view with a row stride, as the pair gives
+        ops.talk_combine(a, talk_d, gate_d[rows], out[:, :H * dv], H, G, dv, 0.8)
+        return out[:, :H * dv].double().cpu()
+
+    a = torch.zeros(n, H * G * dv, dtype=torch.float32, device=DEV)
+    ops.attention_general(qd, kc, vc_, table, seqs, pos, a, ps, 1, H, G, dk, G * dv, scale, window or 0, sink=sink_d, v_share=G)
+    diff = (finish(a) - want).abs().max().item()
+    assert diff <= limit, f"prompt rows differ by {diff:.2e}"
+    last = 40
+    one = torch.zeros(last, H * G * dv, dtype=torch.float32, device=DEV)
+    for r in range(n - last, n):                          # single rows, as decoding brings them
+        ops.attention_general(qd[r:r + 1], kc, vc_, table, seqs[:1], pos[r:r + 1], one[r - n + last:r - n + last + 1], ps, 1,
+                              H, G, dk, G * dv, scale, window or 0, sink=sink_d, v_share=G)
+    diff = (finish(one, slice(n - last, n)) - want[n - last:]).abs().max().item()
+    assert diff <= limit, f"single rows differ by {diff:.2e}"
+    if dtype == torch.bfloat16 and ops.attn_flex_ok(H, G, dk, G * dv, True):
+        per = ops.attn_flex_tokens(H, G)
+        for p0, m, nsplit in ((0, n, 1), (200, 130, 1), (n - 1, 1, 1), (n - 2, 2, 1), (n - 1, 1, 3), (n - 3, 3, 2)):
+            items = torch.tensor([(0, b, min(per, m - b), p0 + b) for b in range(0, m, per)], dtype=torch.int32, device=DEV)
+            scratch = None
+            if nsplit > 1:
+                scratch = torch.zeros(ops.attn_flex_scratch_floats(items.shape[0], H, G, G * dv, nsplit), dtype=torch.float32, device=DEV)
+            af = torch.zeros(m, H * G * dv, dtype=torch.float32, device=DEV)
+            ops.attn_flex(qd[p0:p0 + m], kc, vc_, table, items, af, ps, 1, H, G, dk, G * dv, scale, window or 0, sink=sink_d,
+                          nsplit=nsplit, scratch=scratch, v_share=G)
+            diff = (finish(af, slice(p0, p0 + m)) - want[p0:p0 + m]).abs().max().item()
+            assert diff <= limit, f"tensor-core rows {p0}..{p0 + m} in {nsplit} shares differ by {diff:.2e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("H,G,dk,dv,rd,mag", [(4, 2, 24, 40, 8, 1.07), (6, 2, 32, 16, 32, 1.0), (3, 3, 10, 6, 6, 1.14), (3, 1, 64, 64, 0, 1.0)])
+def test_query_key_preparation_over_the_whole_projection(H, G, dk, dv, rd, mag, dtype):
+    """One norm over all of q (and all of k) with a weight per entry, rotation in halves with a magnitude, the stores of
+    the keys and of a token's values side by side into the pages."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(H * dk)
+    T, ps, eps, base = 37, 8, 1e-5, 5000.0
+    width = (H + G) * dk + G * dv + 5
+    rows = torch.randn(T, width).to(dtype)
+    qw, kw = 1 + 0.3 * torch.randn(H * dk), 1 + 0.3 * torch.randn(G * dk)
+    positions = torch.arange(100, 100 + T)
+    f = base ** (-2.0 * torch.arange(rd // 2, dtype=torch.float64) / rd) if rd else torch.zeros(0, dtype=torch.float64)
+    x = rows.double()
+    qn = (pv.rms(x[:, :H * dk], eps) * qw.double()).view(T, H, dk)
+    kn = (pv.rms(x[:, H * dk:(H + G) * dk], eps) * kw.double()).view(T, G, dk)
+    qn, kn = pv.rotate_halves(qn, positions, f, mag), pv.rotate_halves(kn, positions, f, mag)
+    blocks = -(-(100 + T) // ps)
+    table = torch.randperm(blocks + 2)[:blocks].to(torch.int32).view(1, -1)
+    kc = torch.zeros(blocks + 2, G, ps, dk, dtype=dtype, device=DEV)
+    vc_ = torch.zeros(blocks + 2, 1, ps, G * dv, dtype=dtype, device=DEV)
+    rd_dev = rows.to(DEV)
+    ops.qk_prepare(rd_dev, qw.to(DEV), kw.to(DEV), eps, f.float().to(DEV) if rd else None, rd, False, positions.to(torch.int32).to(DEV),
+                   torch.zeros(T, dtype=torch.int32, device=DEV), table.to(DEV), kc, vc_, ps, 1, H, G, 1, dk, G * dv, whole=True, rot_scale=mag)
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    assert (rd_dev[:, :H * dk].double().cpu().view(T, H, dk) - qn).abs().max().item() <= tol * qn.abs().max().item()
+    for t in range(T):
+        p = 100 + t
+        page = int(table[0, p // ps])
+        assert (kc[page, :, p % ps].double().cpu() - kn[t]).abs().max().item() <= tol * kn.abs().max().item()
+        assert torch.equal(vc_[page, 0, p % ps].cpu(), rows[t, (H + G) * dk:(H + G) * dk + G * dv])
+
+
+@pytest.mark.parametrize("H,n,L", [(4, 24, 6), (3, 64, 16), (2, 5, 1), (8, 32, 8), (2, 160, 12), (1, 128, 3), (6, 16, 5)])
+def test_time_mixing_kernels_in_portions(H, n, L):
+    """The mixes with the row before, the decay, the recurrence with its bonus and the read-out's norm over one sequence
+    cut into portions (2, 1, 17, ...) beside a second sequence, against the plain functions on the whole sequence; the
+    slots start with another request's leavings."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(H * 100 + n)
+    T, d, C, eps = 84, 40, H * n, 1e-5
+    x = torch.randn(T, d)
+    mu = torch.rand(5, d)
+    wr, wk, wv, wg = (torch.randn(C, d) / d ** 0.5 for _ in range(4))
+    w1, w2, w0 = torch.randn(L, d) / d ** 0.5, torch.randn(C, L), torch.empty(C).uniform_(-6, -0.5)
+    u, norm_w = torch.randn(H, n) * 0.7, 1 + 0.2 * torch.randn(C)
+    xd = x.double()
+    prev = torch.cat([torch.zeros(1, d, dtype=torch.float64), xd[:-1]])
+    mix = [xd + (prev - xd) * mu[i].double() for i in range(5)]
+    r, k, v = ((mix[i] @ m.double().t()).view(T, H, n) for i, m in enumerate((wr, wk, wv)))
+    gz = mix[3] @ wg.double().t()
+    dec = torch.exp(-torch.exp(torch.tanh(mix[4] @ w1.double().t()) @ w2.double().t() + w0.double())).view(T, H, n)
+    o = torch.stack([pv.decay_recurrence(r[:, h], k[:, h], v[:, h], dec[:, h], u[h].double()) for h in range(H)], 1)
+    want = pv.rms(o, eps).reshape(T, C) * norm_w.double() * gz * torch.sigmoid(gz) * 0.6
+    assert ops.decay_state_floats(n) == ops.decay_state_floats_of_library(n) >= n * n
+    prev_off = H * ops.decay_state_floats(n)
+    state = torch.randn(3, prev_off + d, device=DEV)                       # stale contents
+    got = torch.zeros(T, C, device=DEV)
+    xdev, other = x.to(DEV), torch.randn(40, d, device=DEV)
+    dev = lambda t: t.to(DEV).contiguous()
+    mu_d, w2t, w0_d, u_d, nw = dev(mu), dev(w2.t()), dev(w0), dev(u), dev(norm_w)
+    ws = [dev(m) for m in (wr, wk, wv, wg)]
+    w1_d = dev(w1)
+    p = po = 0
+    for m in (2, 1, 17, 3, 30, 1, 1, 29):
+        no = min(5, 40 - po)
+        rows = torch.cat([other[po:po + no], xdev[p:p + m]])                 # the other sequence first, in slot 2
+        R = rows.shape[0]
+        ints = lambda *vals: torch.tensor(vals, dtype=torch.int32, device=DEV)
+        positions = torch.cat([torch.arange(po, po + no), torch.arange(p, p + m)]).to(torch.int32).to(DEV)
+        row_seq = torch.tensor([0] * no + [1] * m, dtype=torch.int32, device=DEV)
+        q_start, ctx_len, slots = ints(0, no, R), ints(po + no, p + m), ints(2, 1)
+        mixes = torch.zeros(5, R, d, device=DEV)
+        ops.shift_mix(rows, mu_d, mixes, state, prev_off, positions, row_seq, q_start, slots, 2)
+        proj = [mixes[i] @ ws[i].t() for i in range(4)]                      # the products are not what is tested here
+        z = (mixes[4] @ w1_d.t()).contiguous()
+        xs = torch.zeros(R, 4 * C, device=DEV)
+        ops.time_mix_prepare(proj[0], proj[1], proj[2], z, w2t, w0_d, xs)
+        y = torch.zeros(R, C, device=DEV)
+        ops.decay_scan(xs, u_d, state, y, q_start, ctx_len, slots, 2, H, n)
+        go = torch.zeros(R, C, device=DEV)
+        ops.head_norm_gate(y, proj[3].contiguous(), nw, go, H, n, eps, post=0.6)
+        got[p:p + m] = go[no:]
+        p, po = p + m, po + no
+    assert p == T
+    assert torch.equal(state[1, prev_off:].cpu(), x[-1])                    # the last row waits for the next portion
+    diff = (got.double().cpu() - want).abs().max().item()
+    assert diff <= 2e-4 * max(1.0, want.abs().max().item()), f"differs by {diff:.2e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("T,d,F,E,top,shared", [(37, 64, 40, 7, 3, 24), (5, 96, 48, 4, 4, None), (130, 256, 128, 16, 1, 64), (1, 70, 18, 3, 2, 10),
+                                                (300, 128, 64, 12, 4, 96)])
+def test_routed_feed_forward_kernels(T, d, F, E, top, shared, dtype):
+    """Router (scores, choice, weights, the shared expert's gate), the order by expert, both grouped products and the
+    weighted sum against the plain function; a row alone gives the bits it gives in the batch."""
+    from llm_steadyinfer_b200.parts.moe import RoutedMLP
+    torch.manual_seed(T + E)
+    p = {"hidden_size": d, "intermediate_size": F, "experts": E, "top": top, "scale": 1.7,
+         "shared": None if shared is None else {"intermediate_size": shared}}
+    part = RoutedMLP(p, dtype, DEV)
+    w = {"router": torch.randn(E, d) * 3 / d ** 0.5}
+    for e in range(E):
+        w[f"e{e}.up"], w[f"e{e}.down"] = torch.randn(F, d) * 1.4 / d ** 0.5, torch.randn(d, F) / F ** 0.5
+    if shared is not None:
+        w.update({"shared.up": torch.randn(shared, d) * 1.4 / d ** 0.5, "shared.down": torch.randn(d, shared) / shared ** 0.5,
+                  "shared.sg": torch.randn(1, d) * 2 / d ** 0.5})
+    w = {k: t.to(torch.bfloat16) for k, t in w.items()}
+    assert set(part.weight_shapes()) == set(w)
+    part.load_weights({k: t.to(dtype).to(DEV) for k, t in w.items()})
+    x = torch.randn(T, d).to(dtype)
+    mlp = {"router": {"experts": E, "top": top, "scale": 1.7}, "expert": {"ff": F}, "shared": p["shared"]}
+    wd = {"m." + k: t.double() for k, t in w.items()}
+    want = pv.routed_feed_forward(x.double(), wd, "m.", mlp)
+    margin = pv.routing_margin(x.double(), wd, "m.", mlp)
+
+    class Ctx:
+        def __init__(self):
+            self.scratch, self.status = {}, None
+
+        def buf(self, key, shape, dt):
+            return self.scratch.setdefault((key, tuple(shape), dt), torch.zeros(shape, dtype=dt, device=DEV))
+
+    got = part.forward(x.to(DEV), Ctx()).double().cpu()
+    ok = margin > 1e-5            # both sides read the same rounded rows: only the order of the router's sums differs
+    assert ok.sum() >= T // 2
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    diff = ((got - want)[ok]).abs().max().item()
+    assert diff <= tol * want.abs().max().item(), f"differs by {diff:.2e} of {want.abs().max().item():.1f}"
+    for t in {0, T // 2, T - 1}:                          # a row alone: the same sums in the same order
+        alone = part.forward(x[t:t + 1].to(DEV), Ctx()).double().cpu()
+        assert torch.equal(alone[0], got[t]), f"row {t} alone differs from the row in the batch"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("d", [70, 256, 2048])
+def test_gated_sublayers_join_the_stream(d, dtype):
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(d)
+    T, mult = 11, 0.7
+    resid = torch.randn(T, d) * 3
+    z1, a, z2, f = (torch.randn(T, d).to(dtype) for _ in range(4))
+    b1, b2 = torch.randn(d), torch.randn(d)
+    both = resid.double() + mult * (torch.sigmoid(z1.double() + b1.double()) * a.double() + torch.sigmoid(z2.double() + b2.double()) * f.double())
+    only = resid.double() + mult * torch.sigmoid(z1.double() + b1.double()) * a.double()
+    r = resid.to(DEV).clone()
+    ops.gated_add(r, z1.to(DEV), b1.to(DEV), a.to(DEV), z2.to(DEV), b2.to(DEV), f.to(DEV), mult=mult)
+    assert (r.double().cpu() - both).abs().max().item() <= 2e-6 * both.abs().max().item()
+    r = resid.to(DEV).clone()
+    ops.gated_add(r, z1.to(DEV), b1.to(DEV), a.to(DEV), mult=mult)
+    assert (r.double().cpu() - only).abs().max().item() <= 2e-6 * only.abs().max().item()
+
+
+# ---- the entry point ----------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
+def test_greedy_generation_through_the_entry_point(folders, name):
+    """Greedy tokens through LLM (scheduler, sampler, graphs and steps launched ahead) equal the plain implementation's
+    in 32-bit; bfloat16 runs and mostly agrees."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    cfg, w = pv.read_model_folder(folders[name])
+    prompts = [ru.random_tokens(cfg["vocab"], n, 50 + n) for n in (5, 23, 1, 40)]
+    want = [pv.greedy(cfg, w, p, 12) for p in prompts]
+    for dtype in ("float32", "bfloat16"):
+        for graphs in (True, False):
+            llm = LLM(folders[name], dtype=dtype, max_batch=3, max_seq_len=64, max_gen_len=12, block_size=vc.PAGE_SIZE[name],
+                      max_num_batched_tokens=32, use_cuda_graph=graphs, async_decode=graphs)
+            got = [g.token_ids for g in llm.generate(prompts, SamplingParams(ignore_eos=True))]
+            if dtype == "float32":
+                assert got == want, f"{name} graphs={graphs}: {got} != {want}"
+            else:
+                same = sum(a == b for g, x in zip(got, want) for a, b in zip(g, x))
+                assert same >= 24, f"{name} bf16: only {same} of 48 tokens agree"
+            if graphs:
+                assert llm.runner.graphs_available() and llm.stats["graph_steps"] > 0
+
+
+def test_preemption_recomputes_state_from_the_start(folders):
+    """A pool too small for all requests: some are cut back and computed again; with per-request state nothing of a cut
+    request can be kept, and the tokens still equal the plain implementation's."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    name = "mixed_a"
+    cfg, w = pv.read_model_folder(folders[name])
+    prompts = [ru.random_tokens(cfg["vocab"], n, 90 + n) for n in (30, 28, 26)]
+    want = [pv.greedy(cfg, w, p, 20) for p in prompts]
+    llm = LLM(folders[name], dtype="float32", max_batch=3, max_seq_len=64, max_gen_len=20, block_size=8, num_blocks=14,
+              max_num_batched_tokens=64)
+    res = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [r.token_ids for r in res] == want
+    assert sum(r.num_preemptions for r in res) > 0
+
+
+def test_trace_program(folders, plains, tmp_path):
+    """bin/trace_run as a program on a mixed trace."""
+    name = "mixed_a"
+    reqs = requests_of(name, [40, 7, 90], seed=6)
+    steps = ru.trace_mixed(reqs, 256, seed=1, max_live=3)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders[name], "--dtype", "float32",
+                           "--out", str(out), "--max-tokens", "256", "--page-size", str(vc.PAGE_SIZE[name])],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    pos, vocab = {}, vc.CONFIGS[name]["vocab"]
+    for rec in steps:
+        wanted = sum(len(e["want"]) for e in rec["entries"])
+        rows = None
+        if wanted:
+            rows = torch.from_file(str(out / f"{rec['step']}.f32"), size=wanted * vocab, dtype=torch.float32).view(wanted, vocab)
+        r = 0
+        for e in rec["entries"]:
+            base = pos.get(e["id"], 0)
+            for wpos in e["want"]:
+                assert row_error(rows[r], plains[name].of(reqs[e["id"]])[base + wpos]) <= LIMIT[torch.float32]
+                r += 1
+            pos[e["id"]] = base + len(e["tokens"])
+
+
+def test_command_line_serves_the_design(folders, tmp_path):
+    """The serving program on a Vibunex folder: requests of random lengths arriving over time, sampling, a pool that is
+    used again; and once more on random weights drawn from a configuration file (which then names the decay's rank)."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "m.json"
+    common = ["--num-requests", "12", "--max-batch", "4", "--max-gen", "10", "--prompt-len-dist", "lognormal:30,0.7,2,90",
+              "--output-len-dist", "lognormal:6,0.5,1,10", "--request-rate", "300", "--temperature", "0.8", "--top-p", "0.9",
+              "--ignore-eos", "--kv-block-size", "8", "--num-kv-blocks", "60", "--max-num-batched-tokens", "40",
+              "--max-model-len", "128", "--output-json", str(out)]
+    drawn = vc.clean(vc.MIXED_B)
+    for layer, src in zip(drawn["layers"], vc.MIXED_B["layers"]):
+        layer["mixer"]["right"]["rank"] = src["_rank"]
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(drawn))
+    for source in (["--checkpoint", folders["mixed_a"]], ["--model-config", str(cfg_file)]):
+        proc = subprocess.run([sys.executable, os.path.join(root, "bin", "offline_batch_benchmark"), *source, *common],
+                              capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-3000:]
+        m = json.loads(out.read_text())[0]
+        assert m["completed"] == 12 and m["rejected"] == 0 and m["output_tokens"] > 12 and m["output_tps"] > 0
