@@ -266,6 +266,19 @@ def _nufasun_config():
             "embedding": {"scale": 8.0}, "logit_softcap": 30.0, "loop": {"start": 0, "stop": 8, "times": 1}, "layers": one + one}
 
 
+# ---- the Vibunex design beside the closest existing models ---------------------------------------------------
+_TALKING = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+_TIME_MIX = {"heads": 32, "dim": 64, "rank": 64}
+_ROUTED = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 16, "top": 2, "scale": 1.5}, "shared": {"ff": 2816}}
+
+
+def _vibunex_config():
+    one = {"type": "parallel", "mixer": {"left": _TALKING, "right": _TIME_MIX, "left_scale": 1.0, "right_scale": 0.5}, "mlp": _ROUTED}
+    return {"architecture": "Vibunex", "vocab": MIVORAX_VOCAB, "width": MIVORAX_WIDTH, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "layers": [one] * 8}
+
+
 def mivorax_section(args, section="mivorax") -> int:
     """Prefill of 2,048 tokens and decode (batch 8, context 4,096) of an 8-layer Mivorax model (2 latent attention,
     4 attention with distance bias, 2 state-space layers; width 2,048) and of a Llama model of the same width, depth,
@@ -285,7 +298,13 @@ def mivorax_section(args, section="mivorax") -> int:
     rand_tokens = lambda n: torch.randint(0, MIVORAX_VOCAB, (n,), generator=gen).tolist()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")        # larger than L2: written between timed steps
     results = {}
-    if section == "nufasun":
+    if section == "vibunex":
+        # 8 layers, each a pair of mixers (attention of 16 heads of 128 over 4 key/value heads, weights mixed over the heads;
+        # time mixing of 32 heads of 64 x 64) beside a routed feed-forward (2 of 16 experts of 1,408 and a shared one of 2,816:
+        # 5,632 active a token, as the other models' feed-forwards), beside the Nufasun and Llama models of the same width
+        designs = (("vibunex", _vibunex_config()), ("nufasun", _nufasun_config()), ("llama", _llama_twin()))
+        mixers = {"attention": _TALKING, "time_mix": _TIME_MIX, "feed_forward": _ROUTED}
+    elif section == "nufasun":
         # 8 layers (6 differential attention: 16 heads of two maps of 64 over 4 key/value heads, values of 128, window
         # 4,096; 2 gated delta rule: 16 heads of 128 x 128 over 8 query/key heads; gated feed-forward 5,632) beside the
         # Mivorax and Llama models of the same width, depth and vocabulary
@@ -411,12 +430,13 @@ def main() -> int:
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed region of --section with cudaProfilerStart/Stop "
                          "(for ncu --profile-from-start off)")
-    ap.add_argument("--section", default="all", choices=["all", "decode", "prefill", "mivorax", "nufasun"],
+    ap.add_argument("--section", default="all", choices=["all", "decode", "prefill", "mivorax", "nufasun", "vibunex"],
                     help="run only the device-timed decode steps or only the prefill (for profiling); 'mivorax': prefill "
                          "and decode of a Mivorax model at layer sizes of a real model beside a Llama model of equal "
                          "width, with time per kind of kernel (its own JSON line; the default workload is not run); "
-                         "'nufasun': the same for a Nufasun model beside the Mivorax and Llama models")
-    ap.add_argument("--only-design", default=None, help="--section mivorax / nufasun: run this model alone (for profiling)")
+                         "'nufasun': the same for a Nufasun model beside the Mivorax and Llama models; 'vibunex': the same for a "
+                         "Vibunex model beside the Nufasun and Llama models")
+    ap.add_argument("--only-design", default=None, help="--section mivorax / nufasun / vibunex: run this model alone (for profiling)")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -425,7 +445,7 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     K, W = args.steps, max(3, args.warmup)
-    if args.section in ("mivorax", "nufasun"):
+    if args.section in ("mivorax", "nufasun", "vibunex"):
         return mivorax_section(args, args.section)
 
     import torch

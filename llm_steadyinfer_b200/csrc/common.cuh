@@ -164,6 +164,18 @@ static inline void si_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t
   cudaLaunchKernelEx(&cfg, kernel, P(args)...);
 }
 
+// Shares of a row's entries for kernels that take a block a row: one while the rows alone give every SM two blocks,
+// else as many as bring the blocks there, each share at least one pass of the block's threads.
+static inline int si_row_shares(long long rows, long long entries, int threads) {
+  const long long want = 2LL * si_sm_count();
+  if (rows >= want || rows <= 0) return 1;
+  long long shares = (want + rows - 1) / rows;
+  const long long most = (entries + threads - 1) / threads;
+  if (shares > most) shares = most;
+  if (shares > 64) shares = 64;
+  return shares < 1 ? 1 : (int)shares;
+}
+
 static inline int si_last_error() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : (int)e;

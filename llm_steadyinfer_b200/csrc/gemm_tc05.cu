@@ -496,6 +496,209 @@ static int gemm_tc05_common(const void* x, long long ldx, const void* wmap, CUte
   return si_encode_bf16_2d(am, x, (unsigned long long)M, (unsigned long long)K, (unsigned long long)ldx, 128);
 }
 
+// A grouped product (the experts of a routed feed-forward): the rows of x are ordered by group, group e owning rows
+// offsets[e] .. offsets[e + 1], and rows of group e meet W[e] (W is [E, N, K], described to the TMA unit as [E * N, K]):
+//   out[p, :] = epi(x[p, :] W[e(p)]^T).
+// The same pipeline as the one-CTA kernel; only the tiles differ. After the kernel before it has finished, every block
+// walks the offsets once and lists the row tiles in shared memory (group, first row, rows: a group's rows in tiles of 128
+// from its own first row, so a tile never mixes groups). A tile's box of x starts at its first row wherever that lies
+// (the rows behind the group's end belong to the next group, or are the zeros of an out-of-range read; their sums are
+// not stored), its box of W at row e * N + n0 (rows beyond N likewise). Which row tile holds a row, and where in it, never
+// changes the order of the row's sums.
+#define GROUPED_MAX_ROW_TILES 1024
+template <int STAGES, typename TO, int EPI>
+__global__ void __launch_bounds__(192)
+gemm_tc05_grouped_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
+                         TO* __restrict__ out, long long ldo, const int* __restrict__ offsets, int E, int N, int K, int* status) {
+  constexpr int BM = 128, BN = 256, BK = 64;
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2], acc_empty[2];
+  __shared__ unsigned tmem_slot;
+  __shared__ int row_tiles;
+  __shared__ int tile_group[GROUPED_MAX_ROW_TILES], tile_first[GROUPED_MAX_ROW_TILES];
+  __shared__ short tile_rows[GROUPED_MAX_ROW_TILES];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  unsigned char* As = smem;
+  unsigned char* Bs = smem + STAGES * A_BYTES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int nk = (K + BK - 1) / BK;
+  pdl_trigger();
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }   // 4 epilogue warps
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, 2 * BN);
+  pdl_wait();                                           // the offsets and x come from the kernels before this one
+  if (warp == 2) {                                      // the row tiles: a warp walks the groups, a lane a group at a time
+    int base = 0;
+    bool over = false;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      int a = 0, cnt = 0;
+      if (e < E) { a = offsets[e]; cnt = offsets[e + 1] - a; if (cnt < 0) cnt = 0; }
+      const int mine = (cnt + BM - 1) / BM;
+      int before = mine;                                // tiles of the lanes below this one (inclusive scan, then shifted)
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, before, o);
+        if (lane >= o) before += v;
+      }
+      const int total = __shfl_sync(0xffffffffu, before, 31);
+      before -= mine;
+      for (int i = 0; i < mine; ++i) {
+        const int t = base + before + i;
+        if (t < GROUPED_MAX_ROW_TILES) {
+          tile_group[t] = e; tile_first[t] = a + i * BM; tile_rows[t] = (short)min(BM, cnt - i * BM);
+        } else over = true;
+      }
+      base += total;
+    }
+    over = __any_sync(0xffffffffu, over);
+    if (lane == 0) {
+      row_tiles = over ? 0 : base;
+      if (over) set_status(status, SI_WAIT_LIMIT);      // more row tiles than the table holds: the host refuses such sizes
+    }
+  }
+  tc05_fence_before_sync();
+  __syncthreads();
+  tc05_fence_after_sync();
+  const unsigned tmem = tmem_slot;
+  const int m_tiles = row_tiles;
+  const int tiles = m_tiles * n_tiles;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int mt = tile % m_tiles;
+        const int m0 = tile_first[mt], n0 = tile_group[mt] * N + (tile / m_tiles) * BN;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty_bar[s], (unsigned)(((it / STAGES) - 1) & 1))) {
+            set_status(status, SI_WAIT_LIMIT);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+          tma_load_2d(As + s * A_BYTES, &amap, &full_bar[s], kb * BK, m0);
+          tma_load_2d(Bs + s * B_BYTES, &bmap, &full_bar[s], kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    constexpr unsigned idesc = umma_idesc_bf16(BM, BN, false);
+    const unsigned long long ad0 = umma_desc_sw128(As, 16, 1024), bd0 = umma_desc_sw128(Bs, 16, 1024);
+    int it = 0, local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      if (local >= 2) ok = mbar_wait_warp(&acc_empty[buf], (unsigned)(((local >> 1) - 1) & 1));
+      if (!ok) break;
+      tc05_fence_after_sync();
+      const unsigned acc = tmem + buf * BN;
+      for (int kb = 0; kb < nk; ++kb, ++it) {
+        const int s = it % STAGES;
+        ok = mbar_wait_warp(&full_bar[s], (unsigned)((it / STAGES) & 1));
+        if (!ok) break;
+        tc05_fence_after_sync();
+        const unsigned long long ad = ad0 + (unsigned)s * (A_BYTES / 16), bd = bd0 + (unsigned)s * (B_BYTES / 16);
+        if (elect_one()) {
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            tc05_mma_bf16(acc, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          tc05_commit(&empty_bar[s]);
+          if (kb == nk - 1) tc05_commit(&acc_full[buf]);
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok && lane == 0) set_status(status, SI_WAIT_LIMIT);
+  } else {
+    const int q = warp & 3;
+    const bool vec = (ldo % 8 == 0) && ((uintptr_t)out % 16 == 0);
+    int local = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int mt = tile % m_tiles;
+      const int first = tile_first[mt], rows = tile_rows[mt], n0 = (tile / m_tiles) * BN;
+      if (!mbar_wait_warp(&acc_full[buf], (unsigned)((local >> 1) & 1))) {
+        if (lane == 0) set_status(status, SI_WAIT_LIMIT);
+        break;
+      }
+      tc05_fence_after_sync();
+      const int r = q * 32 + lane;
+      const unsigned src = tmem + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN);
+#pragma unroll 1
+      for (int h = 0; h < BN / 128; ++h) {
+        float v[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32_issue(src + h * 128 + c * 32, v[c]);
+        tmem_ld_wait();
+        if (h == BN / 128 - 1) {
+          tc05_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int n = n0 + h * 128 + c * 32;
+          if (r < rows && n < N) {
+            if (EPI == EPI_RELU2) relu2_row32(v[c]);
+            store_row32<TO>(out + (size_t)(first + r) * ldo + n, v[c], min(32, N - n), vec);
+          }
+        }
+      }
+    }
+  }
+  tc05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 2 * BN);
+}
+
+template <typename TO, int EPI>
+static int launch_grouped(const CUtensorMap& am, const CUtensorMap& bm, void* out, long long ldo, const int* offsets, int P,
+                          int E, int N, int K, int* status, cudaStream_t stream) {
+  constexpr int STAGES = 4;
+  const size_t smem = (size_t)STAGES * (128 * 64 * 2 + 256 * 64 * 2) + 1024;
+  auto k = gemm_tc05_grouped_kernel<STAGES, TO, EPI>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const long long most = ((long long)(P + 127) / 128 + E) * ((N + 255) / 256);      // no more tiles than this, whatever the offsets
+  const int blocks = most < si_sm_count() ? (int)most : si_sm_count();
+  si_launch(k, dim3(blocks), dim3(192), smem, stream, am, bm, (TO*)out, ldo, offsets, E, N, K, status);
+  return si_last_error();
+}
+
+// 1 when the grouped kernel takes P rows in E groups (its table of row tiles holds them whatever the offsets are).
+SI_EXPORT int si_gemm_tc05_grouped_ok(int P, int E) {
+  return P > 0 && E > 0 && (long long)(P + 127) / 128 + E <= GROUPED_MAX_ROW_TILES;
+}
+
+// out[p, :] = act(x[p, :] W[e]^T) for the rows p of group e, offsets[e] <= p < offsets[e + 1] (int32 [E + 1] on the device,
+// offsets[E] <= P). x: [P, K] bf16 rows `ldx` apart; `wmap`: W [E, N, K] described as [E * N, K] with boxes of 256 rows;
+// out [P, N] bf16 or fp32; act 0: none, 1: the square of relu (of the sum rounded to bf16; bf16 out only).
+SI_EXPORT int si_gemm_tc05_grouped(const void* x, long long ldx, const void* wmap, void* out, long long ldo, int out_dtype,
+                                   const int* offsets, int P, int E, int N, int K, int act, int* status, cudaStream_t stream) {
+  if (P <= 0 || N <= 0) return 0;
+  if (!si_gemm_tc05_grouped_ok(P, E) || act < 0 || act > 1 || (act == 1 && out_dtype != SI_BF16)) return -2;
+  CUtensorMap am;
+  const int rc = gemm_tc05_common(x, ldx, wmap, &am, P, K);
+  if (rc) return rc;
+  const CUtensorMap& bm = *(const CUtensorMap*)wmap;
+  if (act == 1) return launch_grouped<bf16, EPI_RELU2>(am, bm, out, ldo, offsets, P, E, N, K, status, stream);
+  if (out_dtype == SI_BF16) return launch_grouped<bf16, EPI_STORE>(am, bm, out, ldo, offsets, P, E, N, K, status, stream);
+  return launch_grouped<float, EPI_STORE>(am, bm, out, ldo, offsets, P, E, N, K, status, stream);
+}
+
 // out_dtype: SI_BF16 or SI_F32. x: [M, K] bf16 rows `ldx` apart. Returns -2 for unsupported sizes.
 // `wmap`: the weight's map with boxes of 256 rows; `wmap_half` (may be null): the one with boxes of 128 rows.
 SI_EXPORT int si_gemm_tc05(const void* x, long long ldx, const void* wmap, const void* wmap_half, void* out, long long ldo,

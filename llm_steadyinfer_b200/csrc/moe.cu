@@ -10,7 +10,8 @@
 //   moe_gemm     C[place] = act(A[row of place] W_e^T) for every place of expert e: a grouped product whose row tiles are
 //                found from the offsets by every block itself (blocks beyond the last tile leave). bf16 on mma.sync
 //                m16n8k16 with fp32 sums, tiles of 64 or 16 rows x 64 columns, three cp.async stages; fp32 on FFMA.
-//                A row's sums run over k in the same order wherever the row lies in its tile.
+//                A row's sums run over k in the same order wherever the row lies in its tile. (Many rows in bf16
+//                go to the tcgen05 grouped product of gemm_tc05.cu instead, behind `moe_gather`.)
 //   moe_combine  out[t] = sum_c weight[t, c] * Y[place(t, c)] (+ gate[t] * shared[t]), the choices in their own order.
 #include "common.cuh"
 #include <math.h>
@@ -38,7 +39,20 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
   for (int e = warp; e < E + extra; e += nwarps) {
     const T* we = w + (size_t)e * d;
     float acc = 0.f;
-    for (int i = lane; i < d; i += 32) acc = fmaf(to_f32<T>(we[i]), xr[i], acc);
+    if (sizeof(T) == 2 && d % 8 == 0 && ((uintptr_t)w & 15) == 0) {      // rows of 16-byte pieces: eight entries a load
+      for (int i = lane * 8; i < d; i += 256) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(we + i);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h2[j]);
+          acc = fmaf(f.x, xr[i + 2 * j], acc);
+          acc = fmaf(f.y, xr[i + 2 * j + 1], acc);
+        }
+      }
+    } else {
+      for (int i = lane; i < d; i += 32) acc = fmaf(to_f32<T>(we[i]), xr[i], acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) sc[e] = acc;
   }
@@ -430,6 +444,40 @@ SI_EXPORT int si_moe_gemm(const void* A, int dtype, long long a_stride, const in
   return si_last_error();
 }
 
+// ---- rows in the order of their places ------------------------------------------------------------------------------------
+// out[p, :] = a[rows[p], :] for every place p (what the TMA-fed grouped product reads as one matrix); 16 bytes a thread
+// and step where rows are so aligned.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_gather_kernel(const T* __restrict__ a, long long a_stride, const int* __restrict__ rows,
+    T* __restrict__ out, long long out_stride, int num_rows, int K, int wide) {
+  pdl_prologue();
+  const long long p = blockIdx.x;
+  int r = rows[p];
+  if (r < 0 || r >= num_rows) r = 0;
+  const T* src = a + (size_t)r * a_stride;
+  T* dst = out + p * out_stride;
+  if (wide) {
+    constexpr int PER = 16 / sizeof(T);
+    for (int i = threadIdx.x; i < K / PER; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < K; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+SI_EXPORT int si_moe_gather(const void* a, int dtype, long long a_stride, const int* rows, void* out, long long out_stride,
+                            int P, int num_rows, int K, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (K <= 0 || num_rows <= 0) return -2;
+  const int es = dtype == SI_BF16 ? 2 : 4, per = 16 / es;
+  const int wide = (K % per == 0 && a_stride % per == 0 && out_stride % per == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)out & 15) == 0) ? 1 : 0;
+  const dim3 grid(P), block(K / per >= 256 ? 256 : 128);
+  if (dtype == SI_BF16)
+    si_launch(moe_gather_kernel<bf16>, grid, block, 0, stream, (const bf16*)a, a_stride, rows, (bf16*)out, out_stride, num_rows, K, wide);
+  else
+    si_launch(moe_gather_kernel<float>, grid, block, 0, stream, (const float*)a, a_stride, rows, (float*)out, out_stride, num_rows, K, wide);
+  return si_last_error();
+}
+
 // ---- combine --------------------------------------------------------------------------------------------------------------
 // out[t, :] = sum_c wts[t, c] * Y[place_of[t, c], :] + gate[t] * shared[t, :]   (gate absent: 1; shared absent: none)
 // Y fp32 or the compute dtype; shared and out in the compute dtype. Sums in fp32, the choices in their own order.
@@ -439,7 +487,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const TY* __restrict__
     int gate_stride, T* __restrict__ out, long long out_stride, int d) {
   pdl_prologue();
   const long long t = blockIdx.x;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += blockDim.x * gridDim.y) {
     float acc = 0.f;
     for (int c = 0; c < top; ++c)
       acc = fmaf(wts[t * top + c], to_f32<TY>(Y[(size_t)place_of[t * top + c] * y_stride + i]), acc);
@@ -453,7 +501,8 @@ SI_EXPORT int si_moe_combine(const void* Y, int y_dtype, long long y_stride, con
                              int dtype, long long out_stride, int rows, int d, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (top <= 0 || d <= 0) return -2;
-  const dim3 grid(rows), block(d >= 1024 ? 256 : 128);
+  const dim3 block(d >= 1024 ? 256 : 128);
+  const dim3 grid(rows, si_row_shares(rows, d, block.x));
   if (dtype == SI_BF16 && y_dtype == SI_F32)
     si_launch(moe_combine_kernel<float, bf16>, grid, block, 0, stream, (const float*)Y, y_stride, place_of, wts, top,
               (const bf16*)shared, shared_stride, gate, gate_stride, (bf16*)out, out_stride, d);

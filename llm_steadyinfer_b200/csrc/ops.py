@@ -1539,10 +1539,49 @@ def moe_plan(ids, E: int, scratch, offsets, row_of, place_of) -> None:
            kernels=1 if P <= MOE_PLAN_CHUNK else 3)
 
 
-def moe_gemm(a, a_rows, w, out, offsets, act: str = "none") -> None:
-    """out[p, :] = act(a[row(p), :] @ w[e]^T) for every place p of expert e (``offsets`` int32 [E + 1] as ``moe_plan``
-    leaves them); row(p) = a_rows[p] (int32 [P]) or p itself (None). ``a`` [*, K] and ``w`` [E, N, K] of one dtype;
-    ``out`` [P, N] in that dtype or fp32. bf16 on the tensor cores with fp32 sums, fp32 in true 32-bit."""
+GROUPED_TC05_MIN_PLACES = 128      # fewer places than this (decode rows, short portions) stay on the mma.sync tiles
+_GROUPED_TC05_ACTS = {"none": 0, "relu2": 1}
+
+
+def moe_gemm_grouped_ok(a, w, out, P: int, act: str = "none") -> bool:
+    """True when ``moe_gemm`` sends this product to the tcgen05 grouped kernel (bf16, many places, K a multiple of 8);
+    a product that gathers its rows then wants the ``gathered`` scratch [P, K]."""
+    E, N, K = w.shape
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and P >= max(GROUPED_TC05_MIN_PLACES, 8 * E)
+            and act in _GROUPED_TC05_ACTS and (act == "none" or out.dtype == torch.bfloat16) and K % 8 == 0
+            and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous()
+            and (P + 127) // 128 + E <= 1024 and gemm_tc05_available())
+
+
+def moe_gather(a, rows, out) -> None:
+    """out[p, :] = a[rows[p], :]: ``a`` [T, K] (rows may have a stride), ``rows`` int32 [P], ``out`` [P, K] of a's dtype."""
+    _cuda(a, rows, out)
+    _i32(rows, "rows")
+    P, K = out.shape
+    _need(a.dim() == 2 and a.shape[1] == K and a.stride(1) == 1 and out.stride(1) == 1 and out.dtype == a.dtype
+          and rows.numel() == P, "moe_gather: a [T, K], rows [P], out [P, K]")
+    f = _fn("moe", "si_moe_gather", [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(rows), _ptr(out), out.stride(0), P, a.shape[0], K, _stream()), f"moe_gather(K={K})")
+
+
+def moe_gemm_tc05(a, w, out, offsets, act: str = "none", status=None) -> None:
+    """The grouped product on the tcgen05 tensor cores: out[p, :] = act(a[p, :] @ w[e]^T) for the places p of expert e
+    (``a`` [P, K] already in the order of the places; ``moe_gemm_grouped_ok`` says when it may be called)."""
+    _cuda(a, w, out, offsets, status)
+    _i32(offsets, "offsets")
+    E, N, K = w.shape
+    P = out.shape[0]
+    _need(a.shape == (P, K) and a.stride(1) == 1 and out.shape == (P, N) and out.stride(1) == 1 and offsets.numel() == E + 1,
+          "moe_gemm_tc05: a [P, K], w [E, N, K], out [P, N]")
+    _need(moe_gemm_grouped_ok(a, w, out, P, act), "moe_gemm_tc05: bf16, at least 128 places, K a multiple of 8, aligned rows")
+    f = _fn("gemm_tc05", "si_gemm_tc05_grouped", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int,
+                                                  _c_int, _c_p, _c_p])
+    _check(f(_ptr(a), a.stride(0), _weight_map(w.view(E * N, K)), _ptr(out), out.stride(0), _dt(out), _ptr(offsets), P, E, N, K,
+             _GROUPED_TC05_ACTS[act], _ptr(status), _stream()), f"moe_gemm_tc05(experts={E}, N={N}, K={K})")
+
+
+def moe_gemm_tiles(a, a_rows, w, out, offsets, act: str = "none") -> None:
+    """``moe_gemm`` on the mma.sync tiles (bf16) or in true 32-bit, whatever the number of places."""
     _cuda(a, a_rows, w, out, offsets)
     _i32(a_rows, "a_rows"); _i32(offsets, "offsets")
     _need(act in MOE_ACTS, f"moe_gemm: act {act!r} is not one of {sorted(MOE_ACTS)}")
@@ -1554,6 +1593,21 @@ def moe_gemm(a, a_rows, w, out, offsets, act: str = "none") -> None:
     f = _fn("moe", "si_moe_gemm", [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(a_rows), _ptr(w), _ptr(out), _dt(out), out.stride(0), _ptr(offsets), P, E, N, K,
              MOE_ACTS[act], _stream()), f"moe_gemm(experts={E}, N={N}, K={K})")
+
+
+def moe_gemm(a, a_rows, w, out, offsets, act: str = "none", gathered=None, status=None) -> None:
+    """out[p, :] = act(a[row(p), :] @ w[e]^T) for every place p of expert e (``offsets`` int32 [E + 1] as ``moe_plan``
+    leaves them); row(p) = a_rows[p] (int32 [P]) or p itself (None). ``a`` [*, K] and ``w`` [E, N, K] of one dtype;
+    ``out`` [P, N] in that dtype or fp32. bf16 on the tensor cores with fp32 sums (tcgen05 where ``moe_gemm_grouped_ok``;
+    a product that gathers then copies its rows into ``gathered`` [P, K] first), fp32 in true 32-bit."""
+    P = out.shape[0]
+    if moe_gemm_grouped_ok(a, w, out, P, act) and (a_rows is None or gathered is not None):
+        if a_rows is not None:
+            moe_gather(a, a_rows, gathered)
+            a = gathered
+        moe_gemm_tc05(a[:P], w, out, offsets, act, status)
+    else:
+        moe_gemm_tiles(a, a_rows, w, out, offsets, act)
 
 
 def moe_combine(y, place_of, wts, out, shared=None, gate=None) -> None:

@@ -220,7 +220,7 @@ SI_EXPORT int si_diff_combine(const void* a, int a_dtype, long long a_stride, co
 // so attention runs with every query head over the values of all G key/value heads side by side (one value "head" of
 // G * dv entries), and this kernel forms the sums, multiplies by sigmoid(gate) and by `post`:
 //   a [T, H, G * dv] (fp32 or the compute dtype), talk fp32 [H, H], gate [T, H * dv] (absent: none), out [T, H * dv].
-// One block a row; everything in fp32.
+// A block takes a row and a share of its entries (blockIdx.y: few rows still fill the device); everything in fp32.
 template <typename TA, typename T>
 __global__ void __launch_bounds__(256) talk_combine_kernel(const TA* __restrict__ a, long long a_stride, const float* __restrict__ talk,
     const T* __restrict__ gate, long long gate_stride, T* __restrict__ out, long long out_stride, int H, int G, int dv, float post) {
@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(256) talk_combine_kernel(const TA* __restrict_
   const long long t = blockIdx.x;
   const TA* ar = a + t * a_stride;
   const int ratio = H / G, wide = G * dv;
-  for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
+  for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < H * dv; e += blockDim.x * gridDim.y) {
     const int h = e / dv, i = e - h * dv;
     const TA* col = ar + (size_t)(h / ratio) * dv + i;
     const float* th = tk + (size_t)h * H;
@@ -248,7 +248,8 @@ SI_EXPORT int si_talk_combine(const void* a, int a_dtype, long long a_stride, co
                               float post, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || dv <= 0 || H > 100) return -2;
-  const dim3 grid(rows), block(H * dv >= 1024 ? 256 : 128);
+  const dim3 block(H * dv >= 1024 ? 256 : 128);
+  const dim3 grid(rows, si_row_shares(rows, H * dv, block.x));
   const size_t smem = (size_t)H * H * sizeof(float);
   if (dtype == SI_BF16 && a_dtype == SI_F32)
     si_launch(talk_combine_kernel<float, __nv_bfloat16>, grid, block, smem, stream, (const float*)a, a_stride, talk,

@@ -4,8 +4,8 @@
 // Three kernels.
 // `shift_mix`: the inputs of the mixer's products. Each product s reads x_t + (x_(t-1) - x_t) * mu_s, where x_(t-1) is
 // the row before in the same sequence: the step's own row, or for a portion's first row what the slot keeps from the
-// step before (zeros at position 0). The block of a portion's first row also renews the slot with the portion's last
-// row, so no two blocks touch a slot.
+// step before (zeros at position 0). The blocks of a portion's first row also renew the slot with the portion's last
+// row, each its own share of the entries, so no two blocks touch an entry of a slot.
 // `time_mix_prepare`: decay = exp(-exp(W2 tanh(z) + w0)) per row and channel (z the low-rank product's first half, fp32
 // arithmetic throughout), written beside fp32 copies of r, k, v as rows [r | k | v | decay].
 // `decay_scan`: the recurrence. The columns of S are independent, so a block takes (sequence, head, a cut of the
@@ -31,7 +31,8 @@ __global__ void __launch_bounds__(256) shift_mix_kernel(const T* __restrict__ x,
   if (seq < 0 || seq >= num_seqs) {                  // a padding row of a fixed-shape step: finite values, nothing kept
     if (seq >= 0 && threadIdx.x == 0) set_status(status, SI_BAD_SEQ);
     for (int m = 0; m < M; ++m)
-      for (int c = threadIdx.x; c < d; c += blockDim.x) out[(size_t)m * out_mat_stride + (size_t)t * d + c] = from_f32<T>(0.f);
+      for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < d; c += blockDim.x * gridDim.y)
+        out[(size_t)m * out_mat_stride + (size_t)t * d + c] = from_f32<T>(0.f);
     return;
   }
   const int first_row = q_start[seq];
@@ -41,7 +42,7 @@ __global__ void __launch_bounds__(256) shift_mix_kernel(const T* __restrict__ x,
   const T* xp = x + (size_t)(t - 1) * x_stride;
   float* keep = state + (size_t)slots[seq] * state_stride + prev_off;
   const T* xl = x + (size_t)(q_start[seq + 1] - 1) * x_stride;       // the portion's last row
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < d; c += blockDim.x * gridDim.y) {
     const float h = to_f32<T>(xr[c]);
     float prev;
     if (!first) prev = to_f32<T>(xp[c]);
@@ -61,7 +62,8 @@ SI_EXPORT int si_shift_mix(const void* x, int dtype, long long x_stride, const f
                            int num_seqs, int d, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (M <= 0 || d <= 0 || prev_off < 0 || prev_off + d > state_stride) return -2;
-  const dim3 grid(num_tokens), block(d >= 1024 ? 256 : 128);
+  const dim3 block(d >= 1024 ? 256 : 128);
+  const dim3 grid(num_tokens, si_row_shares(num_tokens, d, block.x));
   if (dtype == SI_BF16)
     si_launch(shift_mix_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, x_stride, mu, M,
               (__nv_bfloat16*)out, out_mat_stride, state, state_stride, prev_off, positions, row_seq, q_start, slots, num_seqs,
@@ -74,57 +76,67 @@ SI_EXPORT int si_shift_mix(const void* x, int dtype, long long x_stride, const f
 
 // ---- decay and fp32 copies ----------------------------------------------------------------------------------------------
 // r, k, v: rows of C values each in the compute dtype; z [T, L] likewise; w2t fp32 [L, C] (the second low-rank matrix,
-// transposed); w0 fp32 [C]; xs fp32 [T, 4C] = [r | k | v | decay]. A block takes PREP_ROWS rows, a thread a channel at a time.
-#define PREP_ROWS 4
-template <typename T>
+// transposed); w0 fp32 [C]; xs fp32 [T, 4C] = [r | k | v | decay]. A block takes ROWS rows and 256 channels (blockIdx.y),
+// a thread one channel: it walks the L rows of w2t once for all its rows, in the order l = 0, 1, ... whatever ROWS is, so a
+// row's decay does not depend on how many rows the step has.
+template <typename T, int ROWS>
 __global__ void __launch_bounds__(256) time_mix_prepare_kernel(const T* __restrict__ r, long long r_stride, const T* __restrict__ k,
     long long k_stride, const T* __restrict__ v, long long v_stride, const T* __restrict__ z, long long z_stride,
     const float* __restrict__ w2t, const float* __restrict__ w0, float* __restrict__ xs, int rows, int C, int L) {
-  extern __shared__ float th[];                      // [PREP_ROWS][L]: tanh of the rows' low-rank values
+  extern __shared__ float th[];                      // [L][ROWS]: tanh of the rows' low-rank values
   pdl_prologue();
-  const int t0 = blockIdx.x * PREP_ROWS;
-  for (int idx = threadIdx.x; idx < PREP_ROWS * L; idx += blockDim.x) {
+  const int t0 = blockIdx.x * ROWS;
+  for (int idx = threadIdx.x; idx < ROWS * L; idx += blockDim.x) {
     const int rr = idx / L, l = idx - rr * L;
-    th[idx] = t0 + rr < rows ? tanhf(to_f32<T>(z[(size_t)(t0 + rr) * z_stride + l])) : 0.f;
+    th[l * ROWS + rr] = t0 + rr < rows ? tanhf(to_f32<T>(z[(size_t)(t0 + rr) * z_stride + l])) : 0.f;
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float acc[PREP_ROWS];
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float acc[ROWS];
 #pragma unroll
-    for (int rr = 0; rr < PREP_ROWS; ++rr) acc[rr] = 0.f;
-    for (int l = 0; l < L; ++l) {
-      const float w = w2t[(size_t)l * C + c];
+  for (int rr = 0; rr < ROWS; ++rr) acc[rr] = 0.f;
+#pragma unroll 4
+  for (int l = 0; l < L; ++l) {
+    const float w = w2t[(size_t)l * C + c];
 #pragma unroll
-      for (int rr = 0; rr < PREP_ROWS; ++rr) acc[rr] = fmaf(w, th[rr * L + l], acc[rr]);
-    }
-    const float b = w0[c];
-#pragma unroll
-    for (int rr = 0; rr < PREP_ROWS; ++rr) {
-      const int t = t0 + rr;
-      if (t >= rows) break;
-      float* o = xs + (size_t)t * 4 * C;
-      o[c] = to_f32<T>(r[(size_t)t * r_stride + c]);
-      o[C + c] = to_f32<T>(k[(size_t)t * k_stride + c]);
-      o[2 * C + c] = to_f32<T>(v[(size_t)t * v_stride + c]);
-      o[3 * C + c] = expf(-expf(acc[rr] + b));
-    }
+    for (int rr = 0; rr < ROWS; ++rr) acc[rr] = fmaf(w, th[l * ROWS + rr], acc[rr]);
   }
+  const float b = w0[c];
+#pragma unroll
+  for (int rr = 0; rr < ROWS; ++rr) {
+    const int t = t0 + rr;
+    if (t >= rows) break;
+    float* o = xs + (size_t)t * 4 * C;
+    o[c] = to_f32<T>(r[(size_t)t * r_stride + c]);
+    o[C + c] = to_f32<T>(k[(size_t)t * k_stride + c]);
+    o[2 * C + c] = to_f32<T>(v[(size_t)t * v_stride + c]);
+    o[3 * C + c] = expf(-expf(acc[rr] + b));
+  }
+}
+
+template <typename T, int ROWS>
+static void time_mix_prepare_launch(const void* r, long long r_stride, const void* k, long long k_stride, const void* v,
+                                    long long v_stride, const void* z, long long z_stride, const float* w2t, const float* w0,
+                                    float* xs, int rows, int C, int L, cudaStream_t stream) {
+  const dim3 grid((rows + ROWS - 1) / ROWS, (C + 255) / 256), block(256);
+  si_launch(time_mix_prepare_kernel<T, ROWS>, grid, block, (size_t)ROWS * L * sizeof(float), stream, (const T*)r, r_stride,
+            (const T*)k, k_stride, (const T*)v, v_stride, (const T*)z, z_stride, w2t, w0, xs, rows, C, L);
 }
 
 SI_EXPORT int si_time_mix_prepare(const void* r, long long r_stride, const void* k, long long k_stride, const void* v,
                                   long long v_stride, const void* z, long long z_stride, int dtype, const float* w2t,
                                   const float* w0, float* xs, int rows, int C, int L, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (C <= 0 || L <= 0 || L > 2048) return -2;
-  const dim3 grid((rows + PREP_ROWS - 1) / PREP_ROWS), block(256);
-  const size_t smem = (size_t)PREP_ROWS * L * sizeof(float);
-  if (dtype == SI_BF16)
-    si_launch(time_mix_prepare_kernel<__nv_bfloat16>, grid, block, smem, stream, (const __nv_bfloat16*)r, r_stride,
-              (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, (const __nv_bfloat16*)z, z_stride, w2t, w0,
-              xs, rows, C, L);
-  else
-    si_launch(time_mix_prepare_kernel<float>, grid, block, smem, stream, (const float*)r, r_stride, (const float*)k, k_stride,
-              (const float*)v, v_stride, (const float*)z, z_stride, w2t, w0, xs, rows, C, L);
+  if (C <= 0 || L <= 0 || L > 2048 || (C + 255) / 256 > 65535) return -2;
+  // few rows: a row a block, so that the blocks are many; many rows: 16 a block, so that w2t is read once for all of them
+  const bool many = (long long)rows * ((C + 255) / 256) >= 16LL * 4 * si_sm_count();
+#define PREP_LAUNCH(T)                                                                                              \
+  if (many && L <= 768) time_mix_prepare_launch<T, 16>(r, r_stride, k, k_stride, v, v_stride, z, z_stride, w2t, w0, xs, rows, C, L, stream); \
+  else if (many) time_mix_prepare_launch<T, 4>(r, r_stride, k, k_stride, v, v_stride, z, z_stride, w2t, w0, xs, rows, C, L, stream); \
+  else time_mix_prepare_launch<T, 1>(r, r_stride, k, k_stride, v, v_stride, z, z_stride, w2t, w0, xs, rows, C, L, stream);
+  if (dtype == SI_BF16) { PREP_LAUNCH(__nv_bfloat16) } else { PREP_LAUNCH(float) }
+#undef PREP_LAUNCH
   return si_last_error();
 }
 

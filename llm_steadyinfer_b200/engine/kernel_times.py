@@ -33,6 +33,9 @@ KINDS = {
     "gemm_heads": "gemm_heads", "gemm_skinny_relu2": "gemm_skinny_relu2", "gemm_tc05_relu2": "gemm_tc05_relu2", "latent_gather": "latent_gather", "latent_expand_keys": "latent_expand_keys", "causal_conv": "causal_conv", "ssm_scan": "ssm_scan", "gated_part_norm": "gated_part_norm",
     "add_norm": "add_norm", "qk_prepare": "qk_prepare", "diff_combine": "diff_combine", "delta_prepare": "delta_prepare",
     "delta_scan": "delta_scan", "head_norm_gate": "head_norm_gate", "softcap": "softcap", "add_bias": "add_bias",
+    "talk_combine": "talk_combine", "shift_mix": "shift_mix", "time_mix_prepare": "time_mix_prepare", "decay_scan": "decay_scan",
+    "moe_route": "moe_route", "moe_plan": "moe_plan", "moe_gather": "moe_gather", "moe_gemm_tc05": "moe_gemm_tc05",
+    "moe_gemm_tiles": "moe_gemm_tiles", "moe_combine": "moe_combine", "gated_add": "gated_add",
     "glu_limited": "glu_limited", "gemm_skinny_glu_limited": "gemm_skinny_glu_limited", "gemm_tc05_glu_limited": "gemm_tc05_glu_limited",
 }
 

@@ -9,10 +9,12 @@ Per row x:
     out = sum_chosen weight_e * expert_e(x)  +  sigmoid(w_sg . x) * shared(x)      (``shared``: {"intermediate_size": F}
                                                                                    or None; ``shared_gate`` False: no gate)
 On the device, with nothing read back: ``moe_route`` (scores, choice, weights, the shared gate), ``moe_plan`` (pairs ordered
-by expert), two grouped products over the ordered places (the first gathers its rows and applies the activation in its
-epilogue; both on the tensor cores in bfloat16, true 32-bit otherwise), ``moe_combine`` (weighted sum in each row's own order
-of choices, in fp32, the shared expert included). A row's result does not depend on what else is in the batch: places only
-decide where a row lies in a tile, never the order of its sums.
+by expert), two grouped products over the ordered places (the first reads its rows through the order and applies the
+activation in its epilogue; true 32-bit in float32; in bfloat16 on the tensor cores: mma.sync tiles for few places, and
+from 128 places on the TMA-fed tcgen05 grouped kernel behind a gather of the rows), ``moe_combine`` (weighted sum in each
+row's own order of choices, in fp32, the shared expert included). Within a kernel a row's result does not depend on what
+else is in the batch: places only decide where a row lies in a tile, never the order of its sums; which kernel runs
+depends on the number of places, as for every product of the package, and changes the rounding of bfloat16 sums only.
 
 Tensor names below the part's prefix: router, e<i>.up, e<i>.down, shared.up, shared.down, shared.sg.
 """
@@ -72,7 +74,7 @@ class RoutedMLP(FeedForward):
             self.shared.load_weights({n: t[n] for n in self.shared.weight_shapes()})
 
     def kernel_files(self, page_size):
-        return ("moe",) + (self.shared.kernel_files(page_size) if self.shared is not None else ())
+        return ("moe",) + (("gemm_tc05",) if self.dtype == torch.bfloat16 else ()) + (self.shared.kernel_files(page_size) if self.shared is not None else ())
 
     def forward(self, x, ctx):
         T = x.shape[0]
@@ -87,9 +89,10 @@ class RoutedMLP(FeedForward):
         place_of = ctx.buf("moe_place_of", (T, top), torch.int32)
         ops.moe_plan(ids, E, scratch, offsets, row_of, place_of)
         act = ctx.buf("moe_act", (P, self.inter), self.dtype)
-        ops.moe_gemm(x, row_of, self.w_up, act, offsets, act=self.activation)
+        gathered = ctx.buf("moe_x", (P, self.hidden), self.dtype) if ops.moe_gemm_grouped_ok(x, self.w_up, act, P, self.activation) else None
+        ops.moe_gemm(x, row_of, self.w_up, act, offsets, act=self.activation, gathered=gathered, status=ctx.status)
         y = ctx.buf("moe_y", (P, self.hidden), torch.float32)
-        ops.moe_gemm(act, None, self.w_down, y, offsets)
+        ops.moe_gemm(act, None, self.w_down, y, offsets, status=ctx.status)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         out = ctx.buf("moe_out", (T, self.hidden), self.dtype)
         ops.moe_combine(y, place_of, wts, out, shared=shared, gate=gates[:, 0] if gates is not None else None)
