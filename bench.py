@@ -245,10 +245,10 @@ def _mivorax_config():
             "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": one + one}
 
 
-def _llama_twin():
+def _llama_twin(width=MIVORAX_WIDTH, ff=MIVORAX_FF, heads=16, kv_heads=4):
     d = dict(LLAMA_3_1_8B)
-    d.update(hidden_size=MIVORAX_WIDTH, intermediate_size=MIVORAX_FF, num_hidden_layers=8, num_attention_heads=16,
-             num_key_value_heads=4, head_dim=128, vocab_size=MIVORAX_VOCAB)
+    d.update(hidden_size=width, intermediate_size=ff, num_hidden_layers=8, num_attention_heads=heads,
+             num_key_value_heads=kv_heads, head_dim=128, vocab_size=MIVORAX_VOCAB)
     return d
 
 
@@ -273,9 +273,24 @@ _TIME_MIX = {"heads": 32, "dim": 64, "rank": 64}
 _ROUTED = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 16, "top": 2, "scale": 1.5}, "shared": {"ff": 2816}}
 
 
-def _vibunex_config():
-    one = {"type": "parallel", "mixer": {"left": _TALKING, "right": _TIME_MIX, "left_scale": 1.0, "right_scale": 0.5}, "mlp": _ROUTED}
-    return {"architecture": "Vibunex", "vocab": MIVORAX_VOCAB, "width": MIVORAX_WIDTH, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+# other sizes of the Vibunex section (--design-size): width, dense feed-forward of the Llama twin, attention heads and
+# key/value heads of 128, time-mixing heads of 64 x 64, experts, an expert's and the shared expert's size
+_VIBUNEX_SIZES = {"narrow": (1024, 2816, 8, 2, 16, 8, 704, 1408), "base": (MIVORAX_WIDTH, MIVORAX_FF, 16, 4, 32, 16, 1408, 2816),
+                  "wide": (4096, 11264, 32, 4, 64, 16, 2816, 5632)}
+
+
+def _vibunex_parts(size="base"):
+    width, ff, heads, kv, tm_heads, experts, eff, sff = _VIBUNEX_SIZES[size]
+    talking = dict(_TALKING, heads=heads, kv_heads=kv)
+    time_mix = dict(_TIME_MIX, heads=tm_heads)
+    routed = {"kind": "moe", "expert": {"ff": eff}, "router": dict(_ROUTED["router"], experts=experts), "shared": {"ff": sff}}
+    return width, ff, talking, time_mix, routed
+
+
+def _vibunex_config(size="base"):
+    width, _, talking, time_mix, routed = _vibunex_parts(size)
+    one = {"type": "parallel", "mixer": {"left": talking, "right": time_mix, "left_scale": 1.0, "right_scale": 0.5}, "mlp": routed}
+    return {"architecture": "Vibunex", "vocab": MIVORAX_VOCAB, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
             "layers": [one] * 8}
 
 
@@ -298,12 +313,16 @@ def mivorax_section(args, section="mivorax") -> int:
     rand_tokens = lambda n: torch.randint(0, MIVORAX_VOCAB, (n,), generator=gen).tolist()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")        # larger than L2: written between timed steps
     results = {}
+    width, ff = MIVORAX_WIDTH, MIVORAX_FF
     if section == "vibunex":
         # 8 layers, each a pair of mixers (attention of 16 heads of 128 over 4 key/value heads, weights mixed over the heads;
         # time mixing of 32 heads of 64 x 64) beside a routed feed-forward (2 of 16 experts of 1,408 and a shared one of 2,816:
         # 5,632 active a token, as the other models' feed-forwards), beside the Nufasun and Llama models of the same width
-        designs = (("vibunex", _vibunex_config()), ("nufasun", _nufasun_config()), ("llama", _llama_twin()))
-        mixers = {"attention": _TALKING, "time_mix": _TIME_MIX, "feed_forward": _ROUTED}
+        # (--design-size narrow / wide: the same at width 1,024 / 4,096, beside the Llama model of that size)
+        width, ff, talking, time_mix, routed = _vibunex_parts(args.design_size)
+        designs = (("vibunex", _vibunex_config(args.design_size)),) + ((("nufasun", _nufasun_config()),) if args.design_size == "base" else ()) \
+            + (("llama", _llama_twin(width, ff, talking["heads"], talking["kv_heads"])),)
+        mixers = {"attention": talking, "time_mix": time_mix, "feed_forward": routed}
     elif section == "nufasun":
         # 8 layers (6 differential attention: 16 heads of two maps of 64 over 4 key/value heads, values of 128, window
         # 4,096; 2 gated delta rule: 16 heads of 128 x 128 over 8 query/key heads; gated feed-forward 5,632) beside the
@@ -395,7 +414,7 @@ def mivorax_section(args, section="mivorax") -> int:
         torch.cuda.empty_cache()
     pk, pk_src = peaks()
     print(json.dumps({"section": section, "dtype": "bf16", "data": "synthetic: random weights (seed 0), random token ids",
-                      "config": {"width": MIVORAX_WIDTH, "layers": 8, "ff": MIVORAX_FF, "vocab": MIVORAX_VOCAB, "prefill_tokens": PT,
+                      "config": {"width": width, "layers": 8, "ff": ff, "vocab": MIVORAX_VOCAB, "prefill_tokens": PT,
                                  "decode_batch": B, "decode_context": CTX, "page_size": PAGE, "l2": "256 MB written between timed steps",
                                  **mixers},
                       "peaks": pk, "peaks_source": pk_src, "models": results}))
@@ -436,6 +455,8 @@ def main() -> int:
                          "width, with time per kind of kernel (its own JSON line; the default workload is not run); "
                          "'nufasun': the same for a Nufasun model beside the Mivorax and Llama models; 'vibunex': the same for a "
                          "Vibunex model beside the Nufasun and Llama models")
+    ap.add_argument("--design-size", default="base", choices=["narrow", "base", "wide"],
+                    help="--section vibunex: width 1,024 / 2,048 / 4,096 with heads, experts and feed-forward to match")
     ap.add_argument("--only-design", default=None, help="--section mivorax / nufasun / vibunex: run this model alone (for profiling)")
     args = ap.parse_args()
 

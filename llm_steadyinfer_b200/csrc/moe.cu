@@ -253,19 +253,20 @@ __device__ __forceinline__ bool moe_find_tile(const int* __restrict__ offsets, i
 }
 
 #define MOE_BN 64
-#define MOE_BK 32
-#define MOE_PITCH 40          // bf16 entries a tile row in shared memory (32 + 8: fragment loads without bank conflicts)
-#define MOE_STAGES 3
+// A tile row in shared memory holds BK + 8 bf16 entries (fragment loads without bank conflicts). Tiles of 16 places stream
+// an expert's weights for a handful of rows: 64 entries of k a stage and four stages keep enough bytes in flight; tiles of
+// 64 places take 32 and three (static shared memory).
 
 __device__ __forceinline__ void moe_cp16(void* dst, const void* src, int bytes) {       // bytes < 16: the rest is zeros
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes));
 }
 
 // A [*, K] rows (row of place p: a_rows[p], or p itself when a_rows is absent); W [E, N, K]; C [places, N] (bf16 or fp32).
-template <int BM>
+template <int BM, int MOE_BK, int MOE_STAGES>
 __global__ void __launch_bounds__(128) moe_gemm_bf16_kernel(const bf16* __restrict__ A, long long a_stride,
     const int* __restrict__ a_rows, const bf16* __restrict__ W, void* __restrict__ C, long long c_stride, int c_f32,
     const int* __restrict__ offsets, int E, int N, int K, int act, int wide) {
+  constexpr int MOE_PITCH = MOE_BK + 8, KC = MOE_BK / 8;
   __shared__ __align__(16) bf16 As[MOE_STAGES][BM][MOE_PITCH];
   __shared__ __align__(16) bf16 Ws[MOE_STAGES][MOE_BN][MOE_PITCH];
   __shared__ int tile_info[3];
@@ -287,8 +288,8 @@ __global__ void __launch_bounds__(128) moe_gemm_bf16_kernel(const bf16* __restri
   auto load = [&](int kt, int buf) {
     const int k0 = kt * MOE_BK;
     if (wide) {
-      for (int c = threadIdx.x; c < (BM + MOE_BN) * 4; c += blockDim.x) {
-        const int r = c >> 2, kc = (c & 3) * 8;
+      for (int c = threadIdx.x; c < (BM + MOE_BN) * KC; c += blockDim.x) {
+        const int r = c / KC, kc = (c % KC) * 8;
         const int left = K - (k0 + kc);
         const int bytes = left >= 8 ? 16 : (left > 0 ? left * 2 : 0);
         if (r < BM) {
@@ -434,11 +435,11 @@ SI_EXPORT int si_moe_gemm(const void* A, int dtype, long long a_stride, const in
   const int wide = (K % 8 == 0 && a_stride % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) ? 1 : 0;
   if (P < 32LL * E) {                                 // few rows an expert: tiles of 16 places
     const dim3 grid((P + 15) / 16 + E, ny), block(128);
-    si_launch(moe_gemm_bf16_kernel<16>, grid, block, 0, stream, (const bf16*)A, a_stride, a_rows, (const bf16*)W, C, c_stride,
+    si_launch(moe_gemm_bf16_kernel<16, 64, 4>, grid, block, 0, stream, (const bf16*)A, a_stride, a_rows, (const bf16*)W, C, c_stride,
               c_dtype == SI_F32 ? 1 : 0, offsets, E, N, K, act, wide);
   } else {
     const dim3 grid((P + 63) / 64 + E, ny), block(128);
-    si_launch(moe_gemm_bf16_kernel<64>, grid, block, 0, stream, (const bf16*)A, a_stride, a_rows, (const bf16*)W, C, c_stride,
+    si_launch(moe_gemm_bf16_kernel<64, 32, 3>, grid, block, 0, stream, (const bf16*)A, a_stride, a_rows, (const bf16*)W, C, c_stride,
               c_dtype == SI_F32 ? 1 : 0, offsets, E, N, K, act, wide);
   }
   return si_last_error();

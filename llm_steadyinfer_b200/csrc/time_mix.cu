@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(256) time_mix_prepare_kernel(const T* __restri
   float acc[ROWS];
 #pragma unroll
   for (int rr = 0; rr < ROWS; ++rr) acc[rr] = 0.f;
-#pragma unroll 4
+#pragma unroll(ROWS == 1 ? 16 : 4)             // a single row's walk is a chain of loads: many of them in flight
   for (int l = 0; l < L; ++l) {
     const float w = w2t[(size_t)l * C + c];
 #pragma unroll
@@ -150,7 +150,9 @@ __device__ __forceinline__ void tm_cp16(float* dst, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
 }
 
-// Rows a thread (RPT, a multiple of 4) and parts a column (NP, a power of two up to 16, RPT * NP >= n).
+// Rows a thread (RPT, a multiple of 4) and parts a column (NP, a power of two up to 16, RPT * NP >= n). A column is
+// spread over many lanes: a token's step is a chain of dependent instructions in every warp, so a thread keeps few rows
+// and the warps are many (measured: 16 rows a thread and 4 lanes a column took 2.5 times as long as 4 and 16).
 struct DecayShape { int rpt, np; };
 static DecayShape decay_shape(int n) {
   DecayShape s;
@@ -167,12 +169,15 @@ SI_EXPORT long long si_decay_state_floats(int n) {
   return (long long)s.rpt * s.np * n;
 }
 
-// xs fp32 [T, 4C] = [r | k | v | decay], C = H * n; u fp32 [H, n]; y fp32 [T, C]. Shared memory: two buffers of CHUNK
-// tokens of [r: RPT * NP | k: RPT * NP | decay: RPT * NP | v: cols] (rows beyond n stay zero).
+// xs fp32 [T, 4C] = [r | k | v | decay], C = H * n; u fp32 [H, n]; y fp32 [T, C]. Shared memory: two buffers of `chunk`
+// tokens of [r: RPT * NP | k: RPT * NP | decay: RPT * NP | v: cols] (rows beyond n stay zero). A thread keeps its rows two
+// by two (packed fp32 arithmetic): with t = k v_j, the read-out takes r (S + u t) and the state becomes w S + t, four
+// packed operations for two rows.
 template <int RPT, int NP>
 __global__ void __launch_bounds__(256) decay_scan_kernel(const float* __restrict__ xs, long long xs_stride,
     const float* __restrict__ u, float* __restrict__ state, long long state_stride, float* __restrict__ y, long long y_stride,
-    const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ slots, int H, int n, int cols) {
+    const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ slots, int H, int n, int cols,
+    int chunk) {
   extern __shared__ __align__(16) float sm[];
   pdl_prologue();
   const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * cols;
@@ -185,31 +190,37 @@ __global__ void __launch_bounds__(256) decay_scan_kernel(const float* __restrict
   const int C = H * n;
   float* S = state + (size_t)slots[s] * state_stride + (size_t)h * RPT * NP * n + (size_t)(col_ok ? j : 0) * NP + p;
   const size_t s_step = (size_t)n * NP;
-  float st[RPT], uu[RPT];
+  float2 st[RPT / 2], uu[RPT / 2];
 #pragma unroll
-  for (int r = 0; r < RPT; ++r) {
-    st[r] = (col_ok && pos0 > 0) ? S[(size_t)r * s_step] : 0.f;
-    const int i = p * RPT + r;
-    uu[r] = i < n ? u[(size_t)h * n + i] : 0.f;
+  for (int r = 0; r < RPT / 2; ++r) {
+    const bool have = col_ok && pos0 > 0;
+    st[r].x = have ? S[(size_t)(2 * r) * s_step] : 0.f;
+    st[r].y = have ? S[(size_t)(2 * r + 1) * s_step] : 0.f;
+    const int i = p * RPT + 2 * r;
+    uu[r].x = i < n ? u[(size_t)h * n + i] : 0.f;
+    uu[r].y = i + 1 < n ? u[(size_t)h * n + i + 1] : 0.f;
   }
   const int dkp = RPT * NP;
   const int per_tok = 3 * dkp + ((cols + 3) & ~3);
-  for (int idx = threadIdx.x; idx < 2 * DECAY_CHUNK * per_tok; idx += blockDim.x) sm[idx] = 0.f;
+  for (int idx = threadIdx.x; idx < 2 * chunk * per_tok; idx += blockDim.x) sm[idx] = 0.f;
   __syncthreads();
   const size_t head_off = (size_t)h * n;
   const bool wide = n % 4 == 0 && xs_stride % 4 == 0 && ((uintptr_t)xs & 15) == 0;
-  const int unit = wide ? 4 : 1, per_part = n / unit, pieces = 3 * per_part;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  auto fetch = [&](int c0, int buf) {
-    const int cn = min(DECAY_CHUNK, cnt - c0);
+  const int unit = wide ? 4 : 1;
+  auto fetch = [&](int c0, int buf) {           // a token a warp; lanes walk a part's entries, 16 bytes each where aligned
+    const int cn = min(chunk, cnt - c0);
     for (int tt = warp; tt < cn; tt += nwarps) {
-      float* dst = sm + ((size_t)buf * DECAY_CHUNK + tt) * per_tok;
+      float* dst = sm + ((size_t)buf * chunk + tt) * per_tok;
       const float* row = xs + (size_t)(row0 + c0 + tt) * xs_stride + head_off;
-      for (int t = lane; t < pieces; t += 32) {
-        const int part = t / per_part, i = (t - part * per_part) * unit;      // 0 r, 1 k, 2 decay
-        const float* src = row + (size_t)(part == 2 ? 3 : part) * C + i;
-        if (wide) tm_cp16(dst + part * dkp + i, src);
-        else tm_cp4(dst + part * dkp + i, src);
+#pragma unroll
+      for (int part = 0; part < 3; ++part) {                                    // 0 r, 1 k, 2 decay
+        const float* src = row + (size_t)(part == 2 ? 3 : part) * C;
+        float* d = dst + part * dkp;
+        for (int i = lane * unit; i < n; i += 32 * unit) {
+          if (wide) tm_cp16(d + i, src + i);
+          else tm_cp4(d + i, src + i);
+        }
       }
       for (int e = lane; e < cols; e += 32)
         if (j0 + e < n) tm_cp4(dst + 3 * dkp + e, row + (size_t)2 * C + j0 + e);
@@ -218,33 +229,31 @@ __global__ void __launch_bounds__(256) decay_scan_kernel(const float* __restrict
   };
   fetch(0, 0);
   int buf = 0;
-  for (int c0 = 0; c0 < cnt; c0 += DECAY_CHUNK, buf ^= 1) {
-    const int cn = min(DECAY_CHUNK, cnt - c0);
+  for (int c0 = 0; c0 < cnt; c0 += chunk, buf ^= 1) {
+    const int cn = min(chunk, cnt - c0);
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();                            // this chunk has arrived, and everyone is done with the other buffer
-    if (c0 + DECAY_CHUNK < cnt) fetch(c0 + DECAY_CHUNK, buf ^ 1);
-    const float* tok = sm + (size_t)buf * DECAY_CHUNK * per_tok;
+    if (c0 + chunk < cnt) fetch(c0 + chunk, buf ^ 1);
+    const float* tok = sm + (size_t)buf * chunk * per_tok;
     float* yp = y + (size_t)(row0 + c0) * y_stride + head_off + j;
-#pragma unroll 2
+#pragma unroll(RPT <= 8 ? 4 : 2)               // tokens side by side: only the state's own update is a chain from token to token
     for (int tt = 0; tt < cn; ++tt, tok += per_tok, yp += y_stride) {
       const float4* r4 = reinterpret_cast<const float4*>(tok) + p * (RPT / 4);
       const float4* k4 = reinterpret_cast<const float4*>(tok + dkp) + p * (RPT / 4);
       const float4* w4 = reinterpret_cast<const float4*>(tok + 2 * dkp) + p * (RPT / 4);
       const float vj = col_ok ? tok[3 * dkp + jl] : 0.f;
-      float rs = 0.f, bonus = 0.f;               // this thread's parts of r . S[:, j] and of sum_i r_i u_i k_i
+      const float2 v2 = make_float2(vj, vj);
+      float2 ra = make_float2(0.f, 0.f), rb = make_float2(0.f, 0.f);     // this thread's parts of r . (S + diag(u) k v^T)[:, j]
 #pragma unroll
       for (int c = 0; c < RPT / 4; ++c) {
         const float4 rv = r4[c], kv = k4[c], wv = w4[c];
-        const float rr[4] = {rv.x, rv.y, rv.z, rv.w}, kk[4] = {kv.x, kv.y, kv.z, kv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int r = 4 * c + e;
-          rs = fmaf(rr[e], st[r], rs);
-          bonus = fmaf(rr[e] * uu[r], kk[e], bonus);
-          st[r] = fmaf(ww[e], st[r], kk[e] * vj);
-        }
+        const float2 t0 = __fmul2_rn(make_float2(kv.x, kv.y), v2), t1 = __fmul2_rn(make_float2(kv.z, kv.w), v2);
+        ra = __ffma2_rn(make_float2(rv.x, rv.y), __ffma2_rn(uu[2 * c], t0, st[2 * c]), ra);
+        rb = __ffma2_rn(make_float2(rv.z, rv.w), __ffma2_rn(uu[2 * c + 1], t1, st[2 * c + 1]), rb);
+        st[2 * c] = __ffma2_rn(make_float2(wv.x, wv.y), st[2 * c], t0);
+        st[2 * c + 1] = __ffma2_rn(make_float2(wv.z, wv.w), st[2 * c + 1], t1);
       }
-      float o = fmaf(bonus, vj, rs);
+      float o = (ra.x + ra.y) + (rb.x + rb.y);
 #pragma unroll
       for (int off = 1; off < NP; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
       if (p == 0 && col_ok) *yp = o;
@@ -252,7 +261,10 @@ __global__ void __launch_bounds__(256) decay_scan_kernel(const float* __restrict
   }
   if (col_ok) {
 #pragma unroll
-    for (int r = 0; r < RPT; ++r) S[(size_t)r * s_step] = st[r];
+    for (int r = 0; r < RPT / 2; ++r) {
+      S[(size_t)(2 * r) * s_step] = st[r].x;
+      S[(size_t)(2 * r + 1) * s_step] = st[r].y;
+    }
   }
 }
 
@@ -273,7 +285,11 @@ SI_EXPORT int si_decay_scan(const float* xs, long long xs_stride, const float* u
   const int zb = (n + cols - 1) / cols;
   if (zb > 65535) return -2;
   const int threads = ((cols * sh.np + 31) / 32) * 32;
-  const size_t smem = (size_t)2 * DECAY_CHUNK * (3 * sh.np * sh.rpt + ((cols + 3) & ~3)) * sizeof(float);
+  // tokens a buffer: 32, fewer where two buffers of that many would not fit
+  const size_t per_tok = (size_t)(3 * sh.np * sh.rpt + ((cols + 3) & ~3)) * sizeof(float);
+  int chunk = DECAY_CHUNK;
+  while (chunk > 1 && 2 * chunk * per_tok > 200 * 1024) chunk /= 2;
+  const size_t smem = 2 * chunk * per_tok;
   if (smem > 200 * 1024) return -2;
   const dim3 grid(num_seqs, H, zb), block(threads);
 #define DECAY_LAUNCH(R, P)                                                                                           \
@@ -285,7 +301,7 @@ SI_EXPORT int si_decay_scan(const float* xs, long long xs_stride, const float* u
       configured = smem;                                                                                             \
     }                                                                                                                \
     si_launch(decay_scan_kernel<R, P>, grid, block, smem, stream, xs, xs_stride, u, state, state_stride, y, y_stride, \
-              q_start, ctx_len, slots, H, n, cols);                                                                  \
+              q_start, ctx_len, slots, H, n, cols, chunk);                                                           \
   }
   if (sh.np < 16) {
     if (sh.rpt != 4) return -2;
