@@ -74,9 +74,13 @@ __device__ __forceinline__ uint4 ld_cached(const bf16* p) {      // x: small, sh
 template <int MT, int WARPS, int UNROLL, typename TO, bool SWIGLU = false, bool ROPE = false>
 __global__ void __launch_bounds__(WARPS * 32, 512 / (WARPS * 32))
 gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ W, long long ldw,
-                   TO* __restrict__ out, long long ldo, int M, int N, int K, int trigger, const SkinnyRope rope) {
+                   TO* __restrict__ out, long long ldo, int M, int N, int K, int trigger, const SkinnyRope rope,
+                   long long batch_x, long long batch_w, long long batch_o) {
   __shared__ float red[WARPS][MT][32][4];
   if (trigger == 1) pdl_trigger();
+  x += blockIdx.y * batch_x;                    // a batch of products of one shape: blockIdx.y names the product
+  W += blockIdx.y * batch_w;
+  out += blockIdx.y * batch_o;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   // the block's 16 rows of W: n0 .. n0+7 and n1 .. n1+7 (next to each other, or a rotation's two halves)
@@ -256,18 +260,21 @@ static inline bool skinny_four_warps(unsigned blocks) {
 
 template <int WARPS, typename TO, bool SWIGLU, bool ROPE>
 static void skinny_launch(unsigned blocks, cudaStream_t stream, const bf16* xp, long long ldx, const bf16* wp, long long ldw,
-                          TO* out, long long ldo, int M, int N, int K, const SkinnyRope& r) {
+                          TO* out, long long ldo, int M, int N, int K, const SkinnyRope& r, int batch = 1, long long bx = 0,
+                          long long bw = 0, long long bo = 0) {
   constexpr int UNROLL = 8;
-  const int trig = si_pdl_trigger_mode(blocks, (512 / (WARPS * 32)) * si_sm_count());
-  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, TO, SWIGLU, ROPE>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, trig, r);
-  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, TO, SWIGLU, ROPE>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, trig, r);
+  const int trig = si_pdl_trigger_mode(blocks * batch, (512 / (WARPS * 32)) * si_sm_count());
+  const dim3 grid(blocks, batch);
+  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, TO, SWIGLU, ROPE>, grid, dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, trig, r, bx, bw, bo);
+  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, TO, SWIGLU, ROPE>, grid, dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, trig, r, bx, bw, bo);
 }
 
 template <typename TO, bool SWIGLU, bool ROPE>
 static void skinny_dispatch(unsigned blocks, cudaStream_t stream, const bf16* xp, long long ldx, const bf16* wp, long long ldw,
-                            TO* out, long long ldo, int M, int N, int K, const SkinnyRope& r) {
-  if (skinny_four_warps(blocks)) skinny_launch<4, TO, SWIGLU, ROPE>(blocks, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, r);
-  else skinny_launch<8, TO, SWIGLU, ROPE>(blocks, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, r);
+                            TO* out, long long ldo, int M, int N, int K, const SkinnyRope& r, int batch = 1, long long bx = 0,
+                            long long bw = 0, long long bo = 0) {
+  if (skinny_four_warps(blocks * batch)) skinny_launch<4, TO, SWIGLU, ROPE>(blocks, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, r, batch, bx, bw, bo);
+  else skinny_launch<8, TO, SWIGLU, ROPE>(blocks, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, r, batch, bx, bw, bo);
 }
 
 // Largest M this kernel takes.
@@ -284,6 +291,22 @@ SI_EXPORT int si_gemm_skinny(const void* x, long long ldx, const void* W, long l
   const bf16* wp = (const bf16*)W;
   if (out_dtype == SI_BF16) skinny_dispatch<bf16, false, false>(blocks, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, SkinnyRope());
   else skinny_dispatch<float, false, false>(blocks, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, SkinnyRope());
+  return si_last_error();
+}
+
+// `batch` products of one shape in one launch: product b reads x + b * batch_x and W + b * batch_w and writes
+// out + b * batch_o (strides in entries, multiples of 8).
+SI_EXPORT int si_gemm_skinny_batched(const void* x, long long ldx, long long batch_x, const void* W, long long ldw,
+                                     long long batch_w, void* out, long long ldo, long long batch_o, int out_dtype, int batch,
+                                     int M, int N, int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (M > 16 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || (batch_x % 8) || (batch_w % 8) || batch > 65535) return -2;
+  if (((uintptr_t)x % 16) || ((uintptr_t)W % 16)) return -2;
+  const unsigned blocks = (unsigned)((N + 15) / 16);
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)W;
+  if (out_dtype == SI_BF16) skinny_dispatch<bf16, false, false>(blocks, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, SkinnyRope(), batch, batch_x, batch_w, batch_o);
+  else skinny_dispatch<float, false, false>(blocks, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, SkinnyRope(), batch, batch_x, batch_w, batch_o);
   return si_last_error();
 }
 

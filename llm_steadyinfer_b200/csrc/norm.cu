@@ -447,12 +447,50 @@ __global__ void __launch_bounds__(256) gated_add_kernel(float* __restrict__ resi
   }
 }
 
+// The same, eight entries a thread with 16-byte loads (d a multiple of 8, every tensor 16-byte aligned).
+template <typename T>
+__global__ void __launch_bounds__(256) gated_add_vec_kernel(float* __restrict__ resid, const T* __restrict__ z1,
+    const float* __restrict__ b1, const T* __restrict__ a, const T* __restrict__ z2, const float* __restrict__ b2,
+    const T* __restrict__ f, long long n8, int d8, float mult) {
+  pdl_prologue();
+  for (long long i8 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i8 < n8; i8 += (long long)gridDim.x * blockDim.x) {
+    const long long idx = i8 * 8;
+    const int c = (int)(i8 % d8) * 8;
+    Vec8<T> vz, va;
+    Vec8<float> vr, vb;
+    vz.load(z1 + idx); va.load(a + idx); vr.load(resid + idx); vb.load(b1 + c);
+    float s[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s[e] = va.v[e] / (1.f + expf(-(vz.v[e] + vb.v[e])));
+    if (z2) {
+      vz.load(z2 + idx); va.load(f + idx); vb.load(b2 + c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s[e] += va.v[e] / (1.f + expf(-(vz.v[e] + vb.v[e])));
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) vr.v[e] = fmaf(mult, s[e], vr.v[e]);
+    vr.store(resid + idx);
+  }
+}
+
 SI_EXPORT int si_gated_add(float* resid, const void* z1, const float* b1, const void* a, const void* z2, const float* b2,
                            const void* f, int dtype, int rows, int d, float mult, cudaStream_t stream) {
   if (rows <= 0 || d <= 0) return 0;
   if (!z1 || !b1 || !a || ((z2 != nullptr) != (f != nullptr)) || (z2 && !b2)) return -2;
   const long long n = (long long)rows * d;
   const int threads = 256;
+  const uintptr_t all = (uintptr_t)resid | (uintptr_t)z1 | (uintptr_t)b1 | (uintptr_t)a | (uintptr_t)z2 | (uintptr_t)b2 | (uintptr_t)f;
+  if (d % 8 == 0 && (all & 15) == 0) {
+    const long long n8 = n / 8, want8 = (n8 + threads - 1) / threads;
+    const int blocks8 = (int)(want8 < 8LL * si_sm_count() ? want8 : 8LL * si_sm_count());
+    if (dtype == SI_BF16)
+      si_launch(gated_add_vec_kernel<__nv_bfloat16>, dim3(blocks8), dim3(threads), 0, stream, resid, (const __nv_bfloat16*)z1, b1,
+                (const __nv_bfloat16*)a, (const __nv_bfloat16*)z2, b2, (const __nv_bfloat16*)f, n8, d / 8, mult);
+    else
+      si_launch(gated_add_vec_kernel<float>, dim3(blocks8), dim3(threads), 0, stream, resid, (const float*)z1, b1, (const float*)a,
+                (const float*)z2, b2, (const float*)f, n8, d / 8, mult);
+    return si_last_error();
+  }
   const long long want = (n + threads - 1) / threads;
   const int blocks = (int)(want < 8LL * si_sm_count() ? want : 8LL * si_sm_count());
   if (dtype == SI_BF16)

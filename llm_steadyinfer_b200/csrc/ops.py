@@ -637,6 +637,23 @@ def gemm_skinny(a, w, out, checked: bool = False) -> None:
            f"gemm_skinny(M={M}, N={N}, K={K})")
 
 
+def gemm_skinny_batched(a, w, out) -> None:
+    """out[b] = a[b] @ w[b]^T for every b in one launch: ``a`` [B, M, K], ``w`` [B, N, K], ``out`` [B, M, N], M <= 16; each
+    product must be one that ``gemm_skinny`` takes (the caller has asked ``gemm_skinny_ok`` for one of them), and the
+    strides between products multiples of 8 entries."""
+    _cuda(a, w, out)
+    B, M, K = a.shape
+    N = w.shape[1]
+    _need(w.shape == (B, N, K) and out.shape == (B, M, N) and a.stride(2) == 1 and w.stride(2) == 1 and out.stride(2) == 1,
+          "gemm_skinny_batched: shapes")
+    _need(gemm_skinny_ok(a[0], w[0], out[0]) and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0,
+          "gemm_skinny_batched: bf16 inputs, at most 16 rows, K a multiple of 8, 16-byte aligned rows and products")
+    f = _fn("gemm_skinny", "si_gemm_skinny_batched",
+            [_c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(a), a.stride(1), a.stride(0), _ptr(w), w.stride(1), w.stride(0), _ptr(out), out.stride(1), out.stride(0),
+             _dt(out), B, M, N, K, _stream()), f"gemm_skinny_batched(B={B}, M={M}, N={N}, K={K})")
+
+
 def gemm_skinny_relu2(a, w, out, checked: bool = False) -> None:
     """out[M,N] (bf16) = relu(a[M,K] @ w[N,K]^T)^2 for M <= 16: the activation runs in the product's epilogue."""
     _cuda(a, w, out)

@@ -56,12 +56,104 @@ __global__ void __launch_bounds__(256) shift_mix_kernel(const T* __restrict__ x,
   }
 }
 
+// The same, eight entries a thread with 16-byte loads and stores (d, the strides and prev_off multiples of 8 entries, every
+// tensor 16-byte aligned).
+template <typename T> struct TmVec8;
+template <> struct TmVec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct TmVec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) shift_mix_vec_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ mu,
+    int M, T* __restrict__ out, long long out_mat_stride, float* __restrict__ state, long long state_stride, long long prev_off,
+    const int* __restrict__ positions, const int* __restrict__ row_seq, const int* __restrict__ q_start,
+    const int* __restrict__ slots, int num_seqs, int d, int* status) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  const int seq = row_seq[t];
+  const int c_first = (blockIdx.y * blockDim.x + threadIdx.x) * 8, c_step = blockDim.x * gridDim.y * 8;
+  if (seq < 0 || seq >= num_seqs) {                  // a padding row of a fixed-shape step: finite values, nothing kept
+    if (seq >= 0 && threadIdx.x == 0) set_status(status, SI_BAD_SEQ);
+    const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int m = 0; m < M; ++m)
+      for (int c = c_first; c < d; c += c_step) TmVec8<T>::store(out + (size_t)m * out_mat_stride + (size_t)t * d + c, zero);
+    return;
+  }
+  const bool first = t == q_start[seq];
+  const int pos = positions[t];
+  const T* xr = x + (size_t)t * x_stride;
+  const T* xp = x + (size_t)(t - 1) * x_stride;
+  float* keep = state + (size_t)slots[seq] * state_stride + prev_off;
+  const T* xl = x + (size_t)(q_start[seq + 1] - 1) * x_stride;       // the portion's last row
+  for (int c = c_first; c < d; c += c_step) {
+    float h[8], prev[8], diff[8], w[8], o[8];
+    TmVec8<T>::load(xr + c, h);
+    if (!first) TmVec8<T>::load(xp + c, prev);
+    else {
+      if (pos > 0) TmVec8<float>::load(keep + c, prev);
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) prev[e] = 0.f;
+      }
+      float last[8];
+      TmVec8<T>::load(xl + c, last);
+      TmVec8<float>::store(keep + c, last);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) diff[e] = prev[e] - h[e];
+    for (int m = 0; m < M; ++m) {
+      TmVec8<float>::load(mu + (size_t)m * d + c, w);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = fmaf(diff[e], w[e], h[e]);
+      TmVec8<T>::store(out + (size_t)m * out_mat_stride + (size_t)t * d + c, o);
+    }
+  }
+}
+
 SI_EXPORT int si_shift_mix(const void* x, int dtype, long long x_stride, const float* mu, int M, void* out,
                            long long out_mat_stride, float* state, long long state_stride, long long prev_off,
                            const int* positions, const int* row_seq, const int* q_start, const int* slots, int num_tokens,
                            int num_seqs, int d, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (M <= 0 || d <= 0 || prev_off < 0 || prev_off + d > state_stride) return -2;
+  const uintptr_t all = (uintptr_t)x | (uintptr_t)mu | (uintptr_t)out | (uintptr_t)state;
+  if (d % 8 == 0 && x_stride % 8 == 0 && out_mat_stride % 8 == 0 && state_stride % 8 == 0 && prev_off % 8 == 0 && (all & 15) == 0) {
+    const dim3 vblock(d >= 2048 ? 256 : (d >= 1024 ? 128 : 64));
+    const dim3 vgrid(num_tokens, si_row_shares(num_tokens, d / 8, vblock.x));
+    if (dtype == SI_BF16)
+      si_launch(shift_mix_vec_kernel<__nv_bfloat16>, vgrid, vblock, 0, stream, (const __nv_bfloat16*)x, x_stride, mu, M,
+                (__nv_bfloat16*)out, out_mat_stride, state, state_stride, prev_off, positions, row_seq, q_start, slots, num_seqs,
+                d, status);
+    else
+      si_launch(shift_mix_vec_kernel<float>, vgrid, vblock, 0, stream, (const float*)x, x_stride, mu, M, (float*)out,
+                out_mat_stride, state, state_stride, prev_off, positions, row_seq, q_start, slots, num_seqs, d, status);
+    return si_last_error();
+  }
   const dim3 block(d >= 1024 ? 256 : 128);
   const dim3 grid(num_tokens, si_row_shares(num_tokens, d, block.x));
   if (dtype == SI_BF16)

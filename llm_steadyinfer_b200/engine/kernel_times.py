@@ -35,7 +35,7 @@ KINDS = {
     "delta_scan": "delta_scan", "head_norm_gate": "head_norm_gate", "softcap": "softcap", "add_bias": "add_bias",
     "talk_combine": "talk_combine", "shift_mix": "shift_mix", "time_mix_prepare": "time_mix_prepare", "decay_scan": "decay_scan",
     "moe_route": "moe_route", "moe_plan": "moe_plan", "moe_gather": "moe_gather", "moe_gemm_tc05": "moe_gemm_tc05",
-    "moe_gemm_tiles": "moe_gemm_tiles", "moe_combine": "moe_combine", "gated_add": "gated_add",
+    "moe_gemm_tiles": "moe_gemm_tiles", "moe_combine": "moe_combine", "gated_add": "gated_add", "gemm_skinny_batched": "gemm_skinny_batched",
     "glu_limited": "glu_limited", "gemm_skinny_glu_limited": "gemm_skinny_glu_limited", "gemm_tc05_glu_limited": "gemm_tc05_glu_limited",
 }
 

@@ -62,6 +62,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status=None) -> 
     return out
 
 
+def linear_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status=None) -> torch.Tensor:
+    """``out[b] = x[b] @ w[b]^T`` for products of one shape (``x`` [B, M, K], ``w`` [B, N, K], ``out`` [B, M, N]): one
+    launch of the weight-streaming kernel for decode rows, else product by product through ``linear``."""
+    if (USE_SKINNY and x.is_cuda and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and ops.gemm_skinny_ok(x[0], w[0], out[0])):
+        ops.gemm_skinny_batched(x, w, out)
+    else:
+        for b in range(x.shape[0]):
+            linear(x[b], w[b], out[b], status)
+    return out
+
+
 # Many-row products that end a mixer or a feed-forward can add into the residual stream themselves
 # (gemm_tc05_add). Off: measured on the 8B shape the prompt step is 4 to 7 % slower with it, because the epilogue's
 # strided fp32 read-modify-write no longer hides under the next tile's instructions.

@@ -19,7 +19,7 @@ import torch
 
 from ..csrc import ops
 from .base import Mixer, StateNeed, register_mixer
-from .linear import linear
+from .linear import linear, linear_batched
 
 MIXES = ("r", "k", "v", "g", "w")
 
@@ -58,7 +58,7 @@ class TimeMix(Mixer):
     def load_weights(self, t):
         f32 = lambda n: t[n].float().contiguous()
         self.mu = torch.stack([t[f"mu.{m}"].float() for m in MIXES]).contiguous()
-        self.w = {m: t[m].contiguous() for m in ("r", "k", "v", "g")}
+        self.w = torch.stack([t[m] for m in ("r", "k", "v", "g")]).contiguous()      # [4, C, d]: one launch for decode rows
         L = t["w1"].shape[0]
         if t["w2"].shape[1] != L:
             raise ValueError(f"time_mix: w1 has {L} rows but w2 {t['w2'].shape[1]} columns")
@@ -90,8 +90,7 @@ class TimeMix(Mixer):
         ops.shift_mix(x, self.mu, mixes, state, self.prev_off, ctx.positions, ctx.row_seq, ctx.q_start, ctx.slots,
                       ctx.seq_slots, status=ctx.status)
         proj = ctx.buf("tmix_proj", (4, T, C), self.dtype)
-        for i, m in enumerate(("r", "k", "v", "g")):
-            linear(mixes[i], self.w[m], proj[i], ctx.status)
+        linear_batched(mixes[:4], self.w, proj, ctx.status)
         z = ctx.buf("tmix_low", (T, self.L_pad), self.dtype)
         linear(mixes[4], self.w1, z, ctx.status)
         xs = ctx.buf("tmix_xs", (T, 4 * C), torch.float32)
