@@ -268,7 +268,7 @@ def _nufasun_config():
 
 # ---- the Vibunex design beside the closest existing models ---------------------------------------------------
 _TALKING = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-            "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
 _TIME_MIX = {"heads": 32, "dim": 64, "rank": 64}
 _ROUTED = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 16, "top": 2, "scale": 1.5}, "shared": {"ff": 2816}}
 
@@ -289,7 +289,7 @@ def _vibunex_parts(size="base"):
 
 def _vibunex_config(size="base"):
     width, _, talking, time_mix, routed = _vibunex_parts(size)
-    one = {"type": "parallel", "mixer": {"left": talking, "right": time_mix, "left_scale": 1.0, "right_scale": 0.5}, "mlp": routed}
+    one = {"type": "parallel", "mixer": {"left": talking, "right": time_mix, "left_scale": 1.0, "right_scale": 0.6}, "mlp": routed}
     return {"architecture": "Vibunex", "vocab": MIVORAX_VOCAB, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
             "layers": [one] * 8}
 

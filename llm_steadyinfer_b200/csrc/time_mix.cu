@@ -266,7 +266,7 @@ SI_EXPORT long long si_decay_state_floats(int n) {
 // by two (packed fp32 arithmetic): with t = k v_j, the read-out takes r (S + u t) and the state becomes w S + t, four
 // packed operations for two rows.
 template <int RPT, int NP>
-__global__ void __launch_bounds__(256) decay_scan_kernel(const float* __restrict__ xs, long long xs_stride,
+__global__ void __launch_bounds__(256, RPT <= 8 ? 2 : 1) decay_scan_kernel(const float* __restrict__ xs, long long xs_stride,
     const float* __restrict__ u, float* __restrict__ state, long long state_stride, float* __restrict__ y, long long y_stride,
     const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ slots, int H, int n, int cols,
     int chunk) {
@@ -294,7 +294,8 @@ __global__ void __launch_bounds__(256) decay_scan_kernel(const float* __restrict
   }
   const int dkp = RPT * NP;
   const int per_tok = 3 * dkp + ((cols + 3) & ~3);
-  for (int idx = threadIdx.x; idx < 2 * chunk * per_tok; idx += blockDim.x) sm[idx] = 0.f;
+  const int used = min(chunk, cnt) * per_tok;            // what of a buffer this launch's tokens reach (a decode row: one token)
+  for (int idx = threadIdx.x; idx < 2 * used; idx += blockDim.x) sm[idx < used ? idx : chunk * per_tok + idx - used] = 0.f;
   __syncthreads();
   const size_t head_off = (size_t)h * n;
   const bool wide = n % 4 == 0 && xs_stride % 4 == 0 && ((uintptr_t)xs & 15) == 0;
@@ -319,13 +320,50 @@ __global__ void __launch_bounds__(256) decay_scan_kernel(const float* __restrict
     }
     asm volatile("cp.async.commit_group;\n" ::);
   };
-  fetch(0, 0);
+  // Where rows are aligned and a token has at most 32 * DECAY_SLOTS pieces of 16 bytes (its r, k and decay of this head,
+  // then this block's columns of v), every lane knows its pieces once and for all: where they lie in a row of xs and
+  // where they go in a token's shared memory. A token's copy is then a few instructions.
+  constexpr int DECAY_SLOTS = 4;
+  const int pr = n / 4, pieces = 3 * pr + cols / 4;
+  const bool quick = wide && cols % 4 == 0 && j0 + cols <= n && pieces <= 32 * DECAY_SLOTS && 4LL * C < (1LL << 30);
+  int src_off[DECAY_SLOTS], dst_off[DECAY_SLOTS];
+#pragma unroll
+  for (int q = 0; q < DECAY_SLOTS; ++q) {
+    const int idx = lane + 32 * q;
+    src_off[q] = 0;
+    dst_off[q] = -1;
+    if (quick && idx < 3 * pr) {
+      const int part = idx / pr, i = (idx - part * pr) * 4;
+      src_off[q] = (part == 2 ? 3 : part) * C + i;
+      dst_off[q] = part * dkp + i;
+    } else if (quick && idx < pieces) {
+      const int e = (idx - 3 * pr) * 4;
+      src_off[q] = 2 * C + j0 + e;
+      dst_off[q] = 3 * dkp + e;
+    }
+  }
+  auto fetch_quick = [&](int c0, int buf) {
+    const int cn = min(chunk, cnt - c0);
+    for (int tt = warp; tt < cn; tt += nwarps) {
+      float* dst = sm + ((size_t)buf * chunk + tt) * per_tok;
+      const float* row = xs + (size_t)(row0 + c0 + tt) * xs_stride + head_off;
+#pragma unroll
+      for (int q = 0; q < DECAY_SLOTS; ++q)
+        if (dst_off[q] >= 0) tm_cp16(dst + dst_off[q], row + src_off[q]);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  if (quick) fetch_quick(0, 0);
+  else fetch(0, 0);
   int buf = 0;
   for (int c0 = 0; c0 < cnt; c0 += chunk, buf ^= 1) {
     const int cn = min(chunk, cnt - c0);
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();                            // this chunk has arrived, and everyone is done with the other buffer
-    if (c0 + chunk < cnt) fetch(c0 + chunk, buf ^ 1);
+    if (c0 + chunk < cnt) {
+      if (quick) fetch_quick(c0 + chunk, buf ^ 1);
+      else fetch(c0 + chunk, buf ^ 1);
+    }
     const float* tok = sm + (size_t)buf * chunk * per_tok;
     float* yp = y + (size_t)(row0 + c0) * y_stride + head_off + j;
 #pragma unroll(RPT <= 8 ? 4 : 2)               // tokens side by side: only the state's own update is a chain from token to token

@@ -589,6 +589,29 @@ def test_gated_sublayers_join_the_stream(d, dtype):
     assert (r.double().cpu() - only).abs().max().item() <= 2e-6 * only.abs().max().item()
 
 
+@pytest.mark.parametrize("M", [1, 8, 13])
+def test_products_of_one_shape_in_one_launch(M):
+    """The batched weight-streaming product gives each product the bits of its own launch, and both the fp64 product."""
+    from llm_steadyinfer_b200.csrc import ops
+    from llm_steadyinfer_b200.parts.linear import linear_batched
+    torch.manual_seed(M)
+    B, N, K = 4, 200, 96
+    x = torch.randn(5, M, K).to(torch.bfloat16).to(DEV)            # a view of four of five inputs, as the time mixing passes it
+    w = torch.randn(B, N, K).to(torch.bfloat16).to(DEV)
+    out = torch.empty(B, M, N, dtype=torch.bfloat16, device=DEV)
+    linear_batched(x[:4], w, out)
+    for b in range(B):
+        one = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_skinny(x[b], w[b], one)
+        assert torch.equal(one, out[b])
+        want = x[b].double() @ w[b].double().t()
+        assert (out[b].double() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+    odd = torch.empty(B, M, N, dtype=torch.bfloat16, device=DEV)   # rows the kernel refuses go product by product
+    linear_batched(x[:4, :, :90], w[:, :, :90].contiguous(), odd)
+    want = x[0, :, :90].double() @ w[0, :, :90].double().t()
+    assert (odd[0].double() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+
+
 # ---- the entry point ----------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])

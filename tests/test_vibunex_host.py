@@ -21,7 +21,7 @@ def test_configuration_round_trip_and_spec():
     assert config_from_dict(cfg.to_dict()) == cfg
     spec = cfg.model_spec()
     assert spec.order == [0, 1, 2, 3] and len(spec.layers) == 4 and spec.vocab_size == 331 and spec.hidden_size == 96
-    assert all(l.arrangement == "parallel_gated" and l.mixer.kind == "mixer_pair" and l.residual_scale == 0.7 for l in spec.layers)
+    assert all(l.arrangement == "parallel_gated" and l.mixer.kind == "mixer_pair" and l.residual_scale == 0.65 for l in spec.layers)
     assert all(l.mixer_norm.params["scalar"] and l.mixer_gate_name == "rg1" for l in spec.layers) and spec.final_norm.params["scalar"]
     assert spec.layers[1].feed_forward is None and spec.layers[1].feed_forward_norm is None and spec.layers[1].feed_forward_gate_name is None
     ff = spec.layers[0].feed_forward
@@ -29,7 +29,7 @@ def test_configuration_round_trip_and_spec():
     assert ff.params["shared"] == {"intermediate_size": 72} and ff.params["activation"] == "relu2" and not ff.params["renorm"]
     assert spec.layers[2].feed_forward.params["shared"] is None and spec.layers[2].feed_forward.params["top"] == 5
     mx = spec.layers[0].mixer.params
-    assert (mx["left_scale"], mx["right_scale"]) == (1.2, 0.5)
+    assert (mx["left_scale"], mx["right_scale"]) == (1.15, 0.45)
     left, right = mx["left"], mx["right"]
     assert left["kind"] == "talking_attention" and right["kind"] == "time_mix" and right["position"] is None
     assert (left["params"]["num_heads"], left["params"]["num_kv_heads"], left["params"]["head_dim"], left["params"]["value_dim"]) == (4, 2, 24, 16)
@@ -113,7 +113,7 @@ def test_plain_rotation_frequencies():
 
 
 def test_plain_sink_softmax_and_recurrence_closed_forms():
-    # equal scores: each of the i + 1 keys gets 1 / (i + 1 + exp(sink)) -- the sink counts once, unscaled
+    # equal scores: each of the i + 1 keys gets 1 / (i + 1 + exp(sink)) -- one more term in the denominator, exp(sink) as it stands
     q, k = torch.zeros(4, 3, dtype=F64), torch.randn(4, 3, dtype=F64)
     w = pv.sink_softmax_weights(q, k, 0.7, torch.tensor(math.log(2.0), dtype=F64))
     for i in range(4):

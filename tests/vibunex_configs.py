@@ -63,12 +63,12 @@ ONLY_MLP = _model(200, 64, 1e-6, [_layer(_left(2, 1, 8, 8, 8, scaling=None), (2,
 
 # all of it, every layer different
 MIXED_A = _model(331, 96, 1e-5, [
-    _layer(_left(4, 2, 24, 16, 12, base=50000.0), (3, 16), _moe(48, 6, 2, 2.5, shared=72), 1.2, 0.5, rank=6),
+    _layer(_left(4, 2, 24, 16, 12, base=50000.0), (3, 16), _moe(48, 6, 2, 2.5, shared=72), 1.15, 0.45, rank=6),
     _layer(_left(3, 3, 16, 32, 16, scale=0.3, scaling=None), (4, 24), None, 0.7, 1.1, rank=16),
     _layer(_left(6, 1, 8, 16, 4, scaling={"factor": 8.0, "original": 32, "fast": 4.0, "slow": 2.0}), (2, 40),
            _moe(32, 5, 5, 0.6), 1.0, 1.0, rank=3),
     _layer(_left(2, 2, 32, 8, None), (6, 8), _moe(64, 9, 1, 1.0, shared=16), 0.9, 1.4, rank=8),
-], mult=0.7)
+], mult=0.65)
 # sizes in multiples of 16 (what tensor-core kernels take), more heads, wider
 MIXED_B = _model(500, 256, 2e-6, [
     _layer(_left(8, 2, 64, 32, 32, base=250.0), (4, 64), _moe(128, 8, 2, 1.0, shared=128), 1.0, 0.6, rank=32),
