@@ -21,8 +21,9 @@
 
 #define GEN_WARPS 4
 #define GEN_MAX_PER_LANE 20   // key and value sizes up to 640
+#define GEN_WIDE_PER_LANE 32  // a second instance for sizes up to 1,024 (a value head that holds several heads side by side)
 
-template <typename T, typename TO>
+template <typename T, typename TO, int PL = GEN_MAX_PER_LANE>
 __global__ void __launch_bounds__(GEN_WARPS * 32)
 attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
                          const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -49,9 +50,9 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
   const size_t v_stride = v_cache ? dv : dk;
   const T* vbase = v_cache ? v_cache : k_cache;
 
-  float qr[GEN_MAX_PER_LANE], acc[GEN_MAX_PER_LANE];
+  float qr[PL], acc[PL];
 #pragma unroll
-  for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
+  for (int i = 0; i < PL; ++i) {
     const int d = lane + 32 * i;
     qr[i] = d < dk ? to_f32<T>(qh[d]) : 0.f;
     acc[i] = 0.f;
@@ -71,7 +72,7 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
                                        : tok) * v_stride;
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
+    for (int i = 0; i < PL; ++i) {
       const int d = lane + 32 * i;
       if (d < dk) dot += qr[i] * to_f32<T>(kp[d]);
     }
@@ -83,7 +84,7 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
     const float p = expf(dot - m_new);
     l = l * corr + p;
 #pragma unroll
-    for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
+    for (int i = 0; i < PL; ++i) {
       const int d = lane + 32 * i;
       if (d < dv) acc[i] = acc[i] * corr + p * to_f32<T>(vp[d]);
     }
@@ -93,7 +94,7 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
   float* sm = smem + GEN_WARPS * dv;
   float* sl = sm + GEN_WARPS;
 #pragma unroll
-  for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
+  for (int i = 0; i < PL; ++i) {
     const int d = lane + 32 * i;
     if (d < dv) sacc[warp * dv + d] = acc[i];
   }
@@ -124,12 +125,30 @@ SI_EXPORT int si_attention_general(const void* q, int dtype, long long q_row_str
                                    const float* dist_bias, int nd, const float* sink, float softcap, int v_share,
                                    int out_f32, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (dk > 32 * GEN_MAX_PER_LANE || dv > 32 * GEN_MAX_PER_LANE || dk <= 0 || dv <= 0 || KV <= 0 || H % KV) return -2;
+  if (dk > 32 * GEN_WIDE_PER_LANE || dv > 32 * GEN_WIDE_PER_LANE || dk <= 0 || dv <= 0 || KV <= 0 || H % KV) return -2;
   if (!v_cache && dv > dk) return -2;
   if (v_share < 1 || KV % v_share || (v_share > 1 && !v_cache)) return -2;
   if (dist_bias && nd <= 0) return -2;
   dim3 grid(num_tokens, H);
   const size_t smem = (size_t)(GEN_WARPS * dv + 2 * GEN_WARPS) * sizeof(float);
+  if (dk > 32 * GEN_MAX_PER_LANE || dv > 32 * GEN_MAX_PER_LANE) {        // sizes above 640: the kernel with more entries a lane
+    if (dtype == SI_BF16 && out_f32)
+      attention_general_kernel<__nv_bfloat16, float, GEN_WIDE_PER_LANE><<<grid, GEN_WARPS * 32, smem, stream>>>(
+          (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+          block_table, table_width, row_seq, positions, (float*)out, out_row_stride, num_pages,
+          page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
+    else if (dtype == SI_BF16)
+      attention_general_kernel<__nv_bfloat16, __nv_bfloat16, GEN_WIDE_PER_LANE><<<grid, GEN_WARPS * 32, smem, stream>>>(
+          (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+          block_table, table_width, row_seq, positions, (__nv_bfloat16*)out, out_row_stride, num_pages,
+          page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
+    else
+      attention_general_kernel<float, float, GEN_WIDE_PER_LANE><<<grid, GEN_WARPS * 32, smem, stream>>>(
+          (const float*)q, q_row_stride, (const float*)k_cache, (const float*)v_cache, block_table,
+          table_width, row_seq, positions, (float*)out, out_row_stride, num_pages, page_size, num_seqs,
+          H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
+    return si_last_error();
+  }
   if (dtype == SI_BF16 && out_f32)
     attention_general_kernel<__nv_bfloat16, float><<<grid, GEN_WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,

@@ -29,7 +29,7 @@ from . import flex_plan
 from .linear import linear
 
 USE_TENSOR_CORES = True      # bf16 only; False sends bf16 through the plain kernel as well
-MAX_VALUE_WIDTH = 640        # what the general attention kernels take as one value head
+MAX_VALUE_WIDTH = 1024       # what the general attention kernels take as one value head
 
 
 class TalkingAttention(Mixer):

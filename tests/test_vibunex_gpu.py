@@ -272,7 +272,8 @@ def _mixed_heads(q, k, v, scale, sink, talk, window=None):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("H,G,dk,dv,window", [(4, 2, 24, 40, None), (6, 3, 16, 8, 37), (8, 2, 64, 32, None), (3, 1, 10, 6, 64), (5, 5, 32, 16, None)])
+@pytest.mark.parametrize("H,G,dk,dv,window", [(4, 2, 24, 40, None), (6, 3, 16, 8, 37), (8, 2, 64, 32, None), (3, 1, 10, 6, 64), (5, 5, 32, 16, None),
+                                                  (8, 8, 16, 96, None), (4, 4, 8, 250, None)])      # value heads side by side wider than 640
 def test_mixed_attention_far_keys_page_borders_and_the_sink(H, G, dk, dv, window, dtype):
     """Queries built so that one key carries nearly all of a head's weight: keys at page borders, a key far back, and (the
     part offers a window, though this design does not use one) the key just inside and the one just outside it. The values
