@@ -1,7 +1,8 @@
 // bf16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, fp32 accumulation, fp32 online
 // softmax) in the general form of attention_general.cu: key size dk and value size dv of any multiple of 8,
 // values of their own or the first dv entries of the keys (a latent that is key and value), a bias by distance
-// added to the scaled score, a sink per head in the denominator, a soft limit on the scaled score
+// added to the scaled score, a penalty slope[h] * (i - j) taken off it, a query temperature by position (row i's scale
+// times 1 + coef * ln(floor((i + 1) / every) + 1)), a sink per head in the denominator, a soft limit on the scaled score
 // (s <- cap * tanh(s / cap)), key heads that share a value head (v_share neighbouring key heads read one of the
 // KV / v_share value heads), results in fp32 where the caller goes on computing with them. One kernel serves prompt
 // portions and decode rows; for decode the key range of an item can be split over blocks, whose fp32 partial results a second small
@@ -30,6 +31,8 @@ struct FlexParams {
   float* part_ml;           // [item][gy][split][64 rows][2]
   const float* dist_bias; int nd;                // fp32 [nd, H] or nullptr
   const float* sink;                             // fp32 [H] or nullptr
+  const float* slopes;                           // fp32 [H] or nullptr: slope[h] * distance leaves the scaled score
+  float qt_coef; int qt_every;                   // query temperature (every 0: none)
   int num_pages, page_size, num_seqs, H, KV, G, Gb, hparts, dk, dv, dk_pitch;
   int bias_in_smem;         // the distances a key tile can meet are staged in shared memory, tile by tile
   int warps_are_slices;     // items of at most 16 rows whose values are key columns: every warp takes rows 0..15 and a
@@ -167,6 +170,10 @@ attn_flex_kernel(const FlexParams p) {
   const int pos_hi = tok_hi < item.ntok ? item.pos0 + tok_hi : -1;
   const int hh_lo = r_lo % p.Gb, hh_hi = r_hi % p.Gb;
   const int head_lo = head0 + hh_lo, head_hi = head0 + hh_hi;
+  // what a row's raw score is multiplied by beside the scale (its query temperature), and its head's slope (base 2)
+  const float tf_lo = (p.qt_every > 0 && pos_lo >= 0) ? 1.f + p.qt_coef * logf((float)((pos_lo + 1) / p.qt_every + 1)) : 1.f;
+  const float tf_hi = (p.qt_every > 0 && pos_hi >= 0) ? 1.f + p.qt_coef * logf((float)((pos_hi + 1) / p.qt_every + 1)) : 1.f;
+  const float sl_lo = p.slopes ? p.slopes[head_lo] * LOG2E : 0.f, sl_hi = p.slopes ? p.slopes[head_hi] * LOG2E : 0.f;
   const int warp_last_tok = min(item.ntok - 1, (wrow + 15) / p.Gb);
   const int warp_first_tok = wrow / p.Gb;
   const bool warp_active = warp_first_tok < item.ntok && v0 < p.dv;
@@ -220,9 +227,11 @@ attn_flex_kernel(const FlexParams p) {
           float v = -INFINITY;
           if (vis) {
             // tanh(y) = 1 - 2 / (exp(2 y) + 1): absolute error of some 1e-7, which is what counts for a score
-            v = p.cap_log2 > 0.f ? p.cap_log2 * (1.f - __fdividef(2.f, exp2f(s[nt][e] * p.scale_over_cap) + 1.f)) : s[nt][e] * p.scale_log2;
+            const float raw = s[nt][e] * ((e < 2) ? tf_lo : tf_hi);
+            v = p.cap_log2 > 0.f ? p.cap_log2 * (1.f - __fdividef(2.f, exp2f(raw * p.scale_over_cap) + 1.f)) : raw * p.scale_log2;
             if (p.bias_in_smem) v += Bt[(pos - j - dlo) * p.Gb + ((e < 2) ? hh_lo : hh_hi)];
             else if (p.dist_bias) v += p.dist_bias[(size_t)min(pos - j, p.nd - 1) * p.H + ((e < 2) ? head_lo : head_hi)] * LOG2E;
+            v -= ((e < 2) ? sl_lo : sl_hi) * (float)(pos - j);
           }
           s[nt][e] = v;
           if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
@@ -441,11 +450,12 @@ SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cach
                            long long out_stride, int num_pages, int page_size, int num_seqs, int H, int KV, int dk,
                            int dv, float scale, int window, const float* dist_bias, int nd, const float* sink,
                            int nsplit, float* scratch, int max_rows, float softcap, int v_share, int out_is_f32,
-                           int* status, cudaStream_t stream) {
+                           const float* slopes, float qt_coef, int qt_every, int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
   if (!si_attn_flex_ok(H, KV, dk, dv, v_cache != nullptr) || nsplit < 1 || nsplit > 64 || (nsplit > 1 && !scratch)) return -2;
-  if (v_share < 1 || KV % v_share || (v_share > 1 && !v_cache) || softcap < 0.f) return -2;
+  if (v_share < 1 || KV % v_share || (v_share > 1 && !v_cache) || softcap < 0.f || qt_every < 0) return -2;
   FlexParams p;
+  p.slopes = slopes; p.qt_coef = qt_coef; p.qt_every = qt_every;
   p.q = (const bf16*)q; p.q_stride = q_stride;
   p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = block_table; p.table_width = table_width;

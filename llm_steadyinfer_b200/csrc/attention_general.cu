@@ -5,6 +5,8 @@
 //   * values that are the first dv entries of the keys (v_cache == nullptr: a latent that serves as both),
 //   * a bias by distance: bias[min(i - j, nd - 1), head] (fp32 table [nd, H]) added to the scaled score,
 //   * a sink per head: exp(sink[h]) joins the softmax denominator once, with no key and no value,
+//   * a penalty in proportion to the distance: slope[h] * (i - j) taken off the scaled score (fp32 [H]),
+//   * a query temperature by position: the scale of row i is multiplied by 1 + coef * ln(floor((i + 1) / every) + 1),
 //   * a soft limit on the scaled score: s <- softcap * tanh(s / softcap) (before the bias),
 //   * key heads that share a value head: `v_share` neighbouring key heads read one value head (the cache then holds
 //     KV / v_share value heads), as the maps of a differential attention do,
@@ -32,7 +34,8 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
                          TO* __restrict__ out, long long out_row_stride, int num_pages,
                          int page_size, int num_seqs, int H, int KV, int dk, int dv, float scale,
                          int window, const float* __restrict__ dist_bias, int nd,
-                         const float* __restrict__ sink, float softcap, int v_share, int* status) {
+                         const float* __restrict__ sink, float softcap, int v_share,
+                         const float* __restrict__ slopes, float qt_coef, int qt_every, int* status) {
   extern __shared__ float smem[];   // [GEN_WARPS][dv] accumulators, then m[GEN_WARPS], l[GEN_WARPS]
   const int t = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -58,6 +61,8 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
     acc[i] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
+  if (qt_every > 0) scale *= 1.f + qt_coef * logf((float)((pos + 1) / qt_every + 1));
+  const float slope = slopes ? slopes[h] : 0.f;
   const int j0 = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   for (int j = j0 + warp; j <= pos; j += GEN_WARPS) {
     const int slot = j / page_size;
@@ -79,6 +84,7 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
     dot = warp_sum(dot) * scale;
     if (softcap > 0.f) dot = softcap * tanhf(dot / softcap);
     if (dist_bias) dot += dist_bias[(size_t)min(pos - j, nd - 1) * H + h];
+    dot -= slope * (float)(pos - j);
     const float m_new = fmaxf(m, dot);
     const float corr = expf(m - m_new);
     const float p = expf(dot - m_new);
@@ -123,47 +129,31 @@ SI_EXPORT int si_attention_general(const void* q, int dtype, long long q_row_str
                                    long long out_row_stride, int num_pages, int page_size, int num_tokens,
                                    int num_seqs, int H, int KV, int dk, int dv, float scale, int window,
                                    const float* dist_bias, int nd, const float* sink, float softcap, int v_share,
-                                   int out_f32, int* status, cudaStream_t stream) {
+                                   int out_f32, const float* slopes, float qt_coef, int qt_every, int* status,
+                                   cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (dk > 32 * GEN_WIDE_PER_LANE || dv > 32 * GEN_WIDE_PER_LANE || dk <= 0 || dv <= 0 || KV <= 0 || H % KV) return -2;
   if (!v_cache && dv > dk) return -2;
   if (v_share < 1 || KV % v_share || (v_share > 1 && !v_cache)) return -2;
   if (dist_bias && nd <= 0) return -2;
+  if (qt_every < 0) return -2;
   dim3 grid(num_tokens, H);
   const size_t smem = (size_t)(GEN_WARPS * dv + 2 * GEN_WARPS) * sizeof(float);
+#define GEN_LAUNCH(T, TO, PL)                                                                                          \
+  attention_general_kernel<T, TO, PL><<<grid, GEN_WARPS * 32, smem, stream>>>(                                         \
+      (const T*)q, q_row_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_width, row_seq, positions,   \
+      (TO*)out, out_row_stride, num_pages, page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink,     \
+      softcap, v_share, slopes, qt_coef, qt_every, status)
   if (dk > 32 * GEN_MAX_PER_LANE || dv > 32 * GEN_MAX_PER_LANE) {        // sizes above 640: the kernel with more entries a lane
-    if (dtype == SI_BF16 && out_f32)
-      attention_general_kernel<__nv_bfloat16, float, GEN_WIDE_PER_LANE><<<grid, GEN_WARPS * 32, smem, stream>>>(
-          (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-          block_table, table_width, row_seq, positions, (float*)out, out_row_stride, num_pages,
-          page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
-    else if (dtype == SI_BF16)
-      attention_general_kernel<__nv_bfloat16, __nv_bfloat16, GEN_WIDE_PER_LANE><<<grid, GEN_WARPS * 32, smem, stream>>>(
-          (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-          block_table, table_width, row_seq, positions, (__nv_bfloat16*)out, out_row_stride, num_pages,
-          page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
-    else
-      attention_general_kernel<float, float, GEN_WIDE_PER_LANE><<<grid, GEN_WARPS * 32, smem, stream>>>(
-          (const float*)q, q_row_stride, (const float*)k_cache, (const float*)v_cache, block_table,
-          table_width, row_seq, positions, (float*)out, out_row_stride, num_pages, page_size, num_seqs,
-          H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
+    if (dtype == SI_BF16 && out_f32) GEN_LAUNCH(__nv_bfloat16, float, GEN_WIDE_PER_LANE);
+    else if (dtype == SI_BF16) GEN_LAUNCH(__nv_bfloat16, __nv_bfloat16, GEN_WIDE_PER_LANE);
+    else GEN_LAUNCH(float, float, GEN_WIDE_PER_LANE);
     return si_last_error();
   }
-  if (dtype == SI_BF16 && out_f32)
-    attention_general_kernel<__nv_bfloat16, float><<<grid, GEN_WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-        block_table, table_width, row_seq, positions, (float*)out, out_row_stride, num_pages,
-        page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
-  else if (dtype == SI_BF16)
-    attention_general_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, GEN_WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-        block_table, table_width, row_seq, positions, (__nv_bfloat16*)out, out_row_stride, num_pages,
-        page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
-  else
-    attention_general_kernel<float, float><<<grid, GEN_WARPS * 32, smem, stream>>>(
-        (const float*)q, q_row_stride, (const float*)k_cache, (const float*)v_cache, block_table,
-        table_width, row_seq, positions, (float*)out, out_row_stride, num_pages, page_size, num_seqs,
-        H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
+  if (dtype == SI_BF16 && out_f32) GEN_LAUNCH(__nv_bfloat16, float, GEN_MAX_PER_LANE);
+  else if (dtype == SI_BF16) GEN_LAUNCH(__nv_bfloat16, __nv_bfloat16, GEN_MAX_PER_LANE);
+  else GEN_LAUNCH(float, float, GEN_MAX_PER_LANE);
+#undef GEN_LAUNCH
   return si_last_error();
 }
 
@@ -231,8 +221,14 @@ SI_EXPORT int si_kv_store(const void* qkv, int dtype, long long row_stride, cons
 //   page[pos] = [ latent / sqrt(mean(latent^2) + eps) * w | rotate(shared part) ]         (one key "head" of rk + dr)
 //   q_full[h] = [ (left as it is: the absorbed plain part, rk) | rotate(q[h, dq:dq + dr]) ]   for every head
 //   q_exp[h]  = [ q[h, :dq] | rotate(q[h, dq:dq + dr]) ]                                       (optional)
-// rotate(): the first rd of the dr entries in rotate-half pairs (i, i + rd/2), angle pos * inv_freq[i] in fp32;
-// the other dr - rd entries pass.
+// rotate(): the first rd of the dr entries in pairs (i, i + rd/2), or (2i, 2i + 1) when `interleaved`, angle
+// pos * inv_freq[i] in fp32, cosine and sine times `rot_scale`; the other dr - rd entries pass.
+__device__ __forceinline__ float rotated_entry(float u, float v, bool second, float angle, float rot_scale) {
+  float s, c;
+  sincosf(angle, &s, &c);
+  s *= rot_scale; c *= rot_scale;
+  return second ? v * c + u * s : u * c - v * s;
+}
 template <typename T>
 __global__ void latent_prepare_kernel(const T* __restrict__ kv, long long kv_stride, const T* __restrict__ q,
                                       long long q_stride, T* __restrict__ q_full, long long qf_stride,
@@ -240,7 +236,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ kv, long long kv_str
                                       int rd, const int* __restrict__ positions, const int* __restrict__ row_seq,
                                       const int* __restrict__ block_table, int table_width, T* __restrict__ k_cache,
                                       int num_pages, int page_size, int num_seqs, int H, int dq, int dr, int rk,
-                                      int* status) {
+                                      int interleaved, float rot_scale, int* status) {
   __shared__ float red[33];
   pdl_prologue();
   const int t = blockIdx.x;
@@ -256,11 +252,9 @@ __global__ void latent_prepare_kernel(const T* __restrict__ kv, long long kv_str
     const T* src = qrow + (size_t)h * (dq + dr) + dq;
     float y;
     if (i < rd) {
-      const int f = i < half ? i : i - half;
-      float s, c;
-      sincosf(fpos * inv_freq[f], &s, &c);
-      const float u = to_f32<T>(src[f]), v = to_f32<T>(src[f + half]);
-      y = i < half ? u * c - v * s : v * c + u * s;
+      const int f = interleaved ? i >> 1 : (i < half ? i : i - half);
+      const int iu = interleaved ? 2 * f : f, iv = interleaved ? 2 * f + 1 : f + half;
+      y = rotated_entry(to_f32<T>(src[iu]), to_f32<T>(src[iv]), i == iv, fpos * inv_freq[f], rot_scale);
     } else {
       y = to_f32<T>(src[i]);
     }
@@ -288,11 +282,9 @@ __global__ void latent_prepare_kernel(const T* __restrict__ kv, long long kv_str
   for (int i = threadIdx.x; i < dr; i += blockDim.x) {
     float y;
     if (i < rd) {
-      const int f = i < half ? i : i - half;
-      float s, c;
-      sincosf(fpos * inv_freq[f], &s, &c);
-      const float u = to_f32<T>(row[rk + f]), v = to_f32<T>(row[rk + f + half]);
-      y = i < half ? u * c - v * s : v * c + u * s;
+      const int f = interleaved ? i >> 1 : (i < half ? i : i - half);
+      const int iu = interleaved ? 2 * f : f, iv = interleaved ? 2 * f + 1 : f + half;
+      y = rotated_entry(to_f32<T>(row[rk + iu]), to_f32<T>(row[rk + iv]), i == iv, fpos * inv_freq[f], rot_scale);
     } else {
       y = to_f32<T>(row[rk + i]);
     }
@@ -305,8 +297,8 @@ SI_EXPORT int si_latent_prepare(const void* kv, int dtype, long long kv_stride, 
                                 const float* norm_w, float eps,
                                 const float* inv_freq, int rd, const int* positions, const int* row_seq,
                                 const int* block_table, int table_width, void* k_cache, int num_pages, int page_size,
-                                int num_tokens, int num_seqs, int H, int dq, int dr, int rk, int* status,
-                                cudaStream_t stream) {
+                                int num_tokens, int num_seqs, int H, int dq, int dr, int rk, int interleaved,
+                                float rot_scale, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (rd < 0 || rd > dr || rd % 2) return -2;
   if (dtype == SI_BF16)
@@ -314,12 +306,13 @@ SI_EXPORT int si_latent_prepare(const void* kv, int dtype, long long kv_stride, 
               kv_stride, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)q_full, qf_stride, (__nv_bfloat16*)q_exp,
               qe_stride, norm_w, eps, inv_freq,
               rd, positions, row_seq, block_table, table_width, (__nv_bfloat16*)k_cache, num_pages, page_size,
-              num_seqs, H, dq, dr, rk, status);
+              num_seqs, H, dq, dr, rk, interleaved, rot_scale, status);
   else
     si_launch(latent_prepare_kernel<float>, dim3(num_tokens), dim3(128), 0, stream, (const float*)kv, kv_stride,
               (const float*)q, q_stride, (float*)q_full, qf_stride, (float*)q_exp, qe_stride, norm_w, eps, inv_freq, rd,
               positions, row_seq,
-              block_table, table_width, (float*)k_cache, num_pages, page_size, num_seqs, H, dq, dr, rk, status);
+              block_table, table_width, (float*)k_cache, num_pages, page_size, num_seqs, H, dq, dr, rk, interleaved,
+              rot_scale, status);
   return si_last_error();
 }
 

@@ -4,15 +4,19 @@
 //   moe_route    scores z = W_r x (fp32 sums over the row in fp32), s = sigmoid(z) (or softmax over the experts), the `top`
 //                largest (ties: the lower index), weights s * scale (optionally divided by their sum); rows of further
 //                gate matrices behind the router's give sigmoid(w . x) for the same row (a gate on a shared expert).
+//                With a choice bias the `top` largest of s + bias are chosen instead; the weights stay s.
 //   moe_plan     the (row, choice) pairs ordered by expert, rows in step order within an expert: offsets per expert, the
 //                row of every place, the place of every pair. Counting ranks within chunks of 1,024 pairs, so the order
 //                never depends on timing.
 //   moe_gemm     C[place] = act(A[row of place] W_e^T) for every place of expert e: a grouped product whose row tiles are
 //                found from the offsets by every block itself (blocks beyond the last tile leave). bf16 on mma.sync
 //                m16n8k16 with fp32 sums, tiles of 64 or 16 rows x 64 columns, three cp.async stages; fp32 on FFMA.
+//                act "glu_limited": W_e holds gate and up rows in turn (row 2i the gate of entry i, row 2i + 1 its up), and
+//                C[place, i] = g sigmoid(alpha g) (u + 1) with g = min(gate sum, limit), u = clamp(up sum, -limit, limit).
 //                A row's sums run over k in the same order wherever the row lies in its tile. (Many rows in bf16
 //                go to the tcgen05 grouped product of gemm_tc05.cu instead, behind `moe_gather`.)
 //   moe_combine  out[t] = sum_c weight[t, c] * Y[place(t, c)] (+ gate[t] * shared[t]), the choices in their own order.
+//                A choice whose id is not below `real` names an identity expert: its result is the row x[t] itself.
 #include "common.cuh"
 #include <math.h>
 #include <mma.h>
@@ -24,13 +28,14 @@ typedef __nv_bfloat16 bf16;
 // [T, top]; gates fp32 [T, extra]. mode 0: sigmoid scores; 1: softmax over the experts. One block a row.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x, long long x_stride, const T* __restrict__ w,
-    int E, int extra, int d, int top, float scale, int mode, int renorm, int* __restrict__ ids, float* __restrict__ wts,
-    float* __restrict__ gates) {
-  extern __shared__ float rsm[];                       // the row [d], scores [E + extra], used [E]
+    int E, int extra, int d, int top, float scale, int mode, int renorm, const float* __restrict__ choice_bias,
+    int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gates) {
+  extern __shared__ float rsm[];                       // the row [d], scores [E + extra], used [E], choice keys [E]
   pdl_prologue();
   float* xr = rsm;
   float* sc = rsm + d;
   float* used = sc + E + extra;
+  float* key = used + E;
   const long long t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int i = threadIdx.x; i < d; i += blockDim.x) xr[i] = to_f32<T>(x[t * x_stride + i]);
@@ -66,13 +71,20 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
     for (int e = lane; e < E; e += 32) zsum += expf(sc[e] - zmax);
     zsum = warp_sum(zsum);
   }
+  // what the choice goes by: the sums themselves (the scores rise with them), or score + bias where a bias is given
+  for (int e = lane; e < E; e += 32) {
+    float kv = sc[e];
+    if (choice_bias) kv = (mode == 1 ? expf(sc[e] - zmax) / zsum : 1.f / (1.f + expf(-sc[e]))) + choice_bias[e];
+    key[e] = kv;
+  }
+  __syncwarp();
   float total = 0.f, mine = 0.f;
   int my_id = 0;
   for (int c = 0; c < top; ++c) {
     float best = -INFINITY;
     int idx = -1;
     for (int e = lane; e < E; e += 32)
-      if (used[e] == 0.f && (idx < 0 || sc[e] > best)) { best = sc[e]; idx = e; }
+      if (used[e] == 0.f && (idx < 0 || key[e] > best)) { best = key[e]; idx = e; }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
@@ -80,7 +92,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
       if (oi >= 0 && (idx < 0 || ob > best || (ob == best && oi < idx))) { best = ob; idx = oi; }
     }
     if (idx < 0) idx = 0;                              // fewer experts than choices: never with a checked configuration
-    const float s = mode == 1 ? expf(best - zmax) / zsum : 1.f / (1.f + expf(-best));
+    const float z = sc[idx];
+    const float s = mode == 1 ? expf(z - zmax) / zsum : 1.f / (1.f + expf(-z));
     total += s;
     if (lane == c % 32 && c < 32) { mine = s; my_id = idx; }
     if (lane == 0) used[idx] = 1.f;
@@ -93,11 +106,11 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
 }
 
 SI_EXPORT int si_moe_route(const void* x, int dtype, long long x_stride, const void* w, int E, int extra, int d, int top,
-                           float scale, int mode, int renorm, int* ids, float* wts, float* gates, int rows,
-                           cudaStream_t stream) {
+                           float scale, int mode, int renorm, const float* choice_bias, int* ids, float* wts, float* gates,
+                           int rows, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || top > 32 || extra < 0 || d <= 0 || mode < 0 || mode > 1) return -2;
-  const size_t smem = (size_t)(d + 2 * E + extra) * sizeof(float);
+  const size_t smem = (size_t)(d + 3 * E + extra) * sizeof(float);
   if (smem > 160 * 1024) return -2;
   const dim3 grid(rows), block(E + extra >= 8 ? 256 : 128);
 #define ROUTE_LAUNCH(T)                                                                                                \
@@ -108,7 +121,7 @@ SI_EXPORT int si_moe_route(const void* x, int dtype, long long x_stride, const v
       configured = smem;                                                                                             \
     }                                                                                                                \
     si_launch(moe_route_kernel<T>, grid, block, smem, stream, (const T*)x, x_stride, (const T*)w, E, extra, d, top, scale, \
-              mode, renorm, ids, wts, gates);                                                                        \
+              mode, renorm, choice_bias, ids, wts, gates);                                                           \
   }
   if (dtype == SI_BF16) ROUTE_LAUNCH(bf16) else ROUTE_LAUNCH(float)
 #undef ROUTE_LAUNCH
@@ -235,6 +248,12 @@ __device__ __forceinline__ float moe_act(float v, int act) {
   if (act == 3) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));   // gelu_tanh
   return v;
 }
+#define MOE_ACT_GLU_LIMITED 4
+// gate and up sums of one entry (neighbouring columns of the product): g sigmoid(alpha g) (u + 1) within the limit
+__device__ __forceinline__ float moe_glu_limited(float gate, float up, float limit, float alpha) {
+  const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+  return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
 
 // The tile a block takes: expert, first place, places. Thread 0 walks the offsets; false: no tile is left for this block.
 __device__ __forceinline__ bool moe_find_tile(const int* __restrict__ offsets, int E, int BM, int tile, int* sm3) {
@@ -265,7 +284,7 @@ __device__ __forceinline__ void moe_cp16(void* dst, const void* src, int bytes) 
 template <int BM, int BN, int MOE_BK, int MOE_STAGES>
 __global__ void __launch_bounds__(128) moe_gemm_bf16_kernel(const bf16* __restrict__ A, long long a_stride,
     const int* __restrict__ a_rows, const bf16* __restrict__ W, void* __restrict__ C, long long c_stride, int c_f32,
-    const int* __restrict__ offsets, int E, int N, int K, int act, int wide) {
+    const int* __restrict__ offsets, int E, int N, int K, int act, int wide, float limit, float alpha) {
   constexpr int MOE_PITCH = MOE_BK + 8, KC = MOE_BK / 8;
   __shared__ __align__(16) bf16 As[MOE_STAGES][BM][MOE_PITCH];
   __shared__ __align__(16) bf16 Ws[MOE_STAGES][BN][MOE_PITCH];
@@ -352,6 +371,14 @@ __global__ void __launch_bounds__(128) moe_gemm_bf16_kernel(const bf16* __restri
       const int r = wr0 + g + half * 8;
       if (r >= rows) continue;
       const size_t place = (size_t)(first + r);
+      if (act == MOE_ACT_GLU_LIMITED) {                 // the thread's two columns are an entry's gate and up
+        const int n = n0 + wn0 + nt * 8 + 2 * tq;
+        if (n + 1 >= N) continue;
+        const float v = moe_glu_limited(acc[nt][half * 2], acc[nt][half * 2 + 1], limit, alpha);
+        if (c_f32) reinterpret_cast<float*>(C)[place * c_stride + (n >> 1)] = v;
+        else reinterpret_cast<bf16*>(C)[place * c_stride + (n >> 1)] = __float2bfloat16_rn(v);
+        continue;
+      }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const int n = n0 + wn0 + nt * 8 + 2 * tq + c;
@@ -367,7 +394,7 @@ __global__ void __launch_bounds__(128) moe_gemm_bf16_kernel(const bf16* __restri
 // True 32-bit: tiles of 32 places x 64 columns, 16 entries of k at a time, a thread 2 x 4 results.
 __global__ void __launch_bounds__(256) moe_gemm_f32_kernel(const float* __restrict__ A, long long a_stride,
     const int* __restrict__ a_rows, const float* __restrict__ W, float* __restrict__ C, long long c_stride,
-    const int* __restrict__ offsets, int E, int N, int K, int act) {
+    const int* __restrict__ offsets, int E, int N, int K, int act, float limit, float alpha) {
   constexpr int BM = 32, BK = 16;
   __shared__ float As[BK][BM + 1];
   __shared__ float Ws[BK][MOE_BN + 1];
@@ -411,6 +438,14 @@ __global__ void __launch_bounds__(256) moe_gemm_f32_kernel(const float* __restri
   for (int rr = 0; rr < 2; ++rr) {
     const int r = ty * 2 + rr;
     if (r >= rows) continue;
+    if (act == MOE_ACT_GLU_LIMITED) {
+#pragma unroll
+      for (int c = 0; c < 4; c += 2) {
+        const int n = n0 + tx * 4 + c;
+        if (n + 1 < N) C[(size_t)(first + r) * c_stride + (n >> 1)] = moe_glu_limited(acc[rr][c], acc[rr][c + 1], limit, alpha);
+      }
+      continue;
+    }
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int n = n0 + tx * 4 + c;
@@ -420,16 +455,18 @@ __global__ void __launch_bounds__(256) moe_gemm_f32_kernel(const float* __restri
 }
 
 SI_EXPORT int si_moe_gemm(const void* A, int dtype, long long a_stride, const int* a_rows, const void* W, void* C, int c_dtype,
-                          long long c_stride, const int* offsets, int P, int E, int N, int K, int act, cudaStream_t stream) {
+                          long long c_stride, const int* offsets, int P, int E, int N, int K, int act, float limit, float alpha,
+                          cudaStream_t stream) {
   if (P <= 0) return 0;
-  if (E <= 0 || N <= 0 || K <= 0 || act < 0 || act > 3) return -2;
+  if (E <= 0 || N <= 0 || K <= 0 || act < 0 || act > MOE_ACT_GLU_LIMITED) return -2;
+  if (act == MOE_ACT_GLU_LIMITED && (N % 2 || !(limit > 0.f))) return -2;
   const int ny = (N + MOE_BN - 1) / MOE_BN;
   if (ny > 65535) return -2;
   if (dtype == SI_F32) {
     if (c_dtype != SI_F32) return -2;
     const dim3 grid((P + 31) / 32 + E, ny), block(256);
     si_launch(moe_gemm_f32_kernel, grid, block, 0, stream, (const float*)A, a_stride, a_rows, (const float*)W, (float*)C, c_stride,
-              offsets, E, N, K, act);
+              offsets, E, N, K, act, limit, alpha);
     return si_last_error();
   }
   const int wide = (K % 8 == 0 && a_stride % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) ? 1 : 0;
@@ -437,11 +474,11 @@ SI_EXPORT int si_moe_gemm(const void* A, int dtype, long long a_stride, const in
     // (32 columns a block, twice the blocks, measured no faster: 0.61 against 0.58 ms for the 16 launches of a decode step)
     const dim3 grid((P + 15) / 16 + E, ny), block(128);
     si_launch(moe_gemm_bf16_kernel<16, 64, 64, 4>, grid, block, 0, stream, (const bf16*)A, a_stride, a_rows, (const bf16*)W, C, c_stride,
-              c_dtype == SI_F32 ? 1 : 0, offsets, E, N, K, act, wide);
+              c_dtype == SI_F32 ? 1 : 0, offsets, E, N, K, act, wide, limit, alpha);
   } else {
     const dim3 grid((P + 63) / 64 + E, ny), block(128);
     si_launch(moe_gemm_bf16_kernel<64, 64, 32, 3>, grid, block, 0, stream, (const bf16*)A, a_stride, a_rows, (const bf16*)W, C, c_stride,
-              c_dtype == SI_F32 ? 1 : 0, offsets, E, N, K, act, wide);
+              c_dtype == SI_F32 ? 1 : 0, offsets, E, N, K, act, wide, limit, alpha);
   }
   return si_last_error();
 }
@@ -486,13 +523,17 @@ SI_EXPORT int si_moe_gather(const void* a, int dtype, long long a_stride, const 
 template <typename TY, typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const TY* __restrict__ Y, long long y_stride, const int* __restrict__ place_of,
     const float* __restrict__ wts, int top, const T* __restrict__ shared, long long shared_stride, const float* __restrict__ gate,
-    int gate_stride, T* __restrict__ out, long long out_stride, int d) {
+    int gate_stride, T* __restrict__ out, long long out_stride, int d, const int* __restrict__ ids, int real,
+    const T* __restrict__ x, long long x_stride) {
   pdl_prologue();
   const long long t = blockIdx.x;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += blockDim.x * gridDim.y) {
     float acc = 0.f;
-    for (int c = 0; c < top; ++c)
-      acc = fmaf(wts[t * top + c], to_f32<TY>(Y[(size_t)place_of[t * top + c] * y_stride + i]), acc);
+    for (int c = 0; c < top; ++c) {
+      const bool same = ids && ids[t * top + c] >= real;           // an identity expert: the row itself
+      const float y = same ? to_f32<T>(x[t * x_stride + i]) : to_f32<TY>(Y[(size_t)place_of[t * top + c] * y_stride + i]);
+      acc = fmaf(wts[t * top + c], y, acc);
+    }
     if (shared) acc = fmaf(gate ? gate[t * gate_stride] : 1.f, to_f32<T>(shared[t * shared_stride + i]), acc);
     out[t * out_stride + i] = from_f32<T>(acc);
   }
@@ -500,20 +541,21 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const TY* __restrict__
 
 SI_EXPORT int si_moe_combine(const void* Y, int y_dtype, long long y_stride, const int* place_of, const float* wts, int top,
                              const void* shared, long long shared_stride, const float* gate, int gate_stride, void* out,
-                             int dtype, long long out_stride, int rows, int d, cudaStream_t stream) {
+                             int dtype, long long out_stride, int rows, int d, const int* ids, int real, const void* x,
+                             long long x_stride, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (top <= 0 || d <= 0) return -2;
+  if (top <= 0 || d <= 0 || (ids && !x)) return -2;
   const dim3 block(d >= 1024 ? 256 : 128);
   const dim3 grid(rows, si_row_shares(rows, d, block.x));
   if (dtype == SI_BF16 && y_dtype == SI_F32)
     si_launch(moe_combine_kernel<float, bf16>, grid, block, 0, stream, (const float*)Y, y_stride, place_of, wts, top,
-              (const bf16*)shared, shared_stride, gate, gate_stride, (bf16*)out, out_stride, d);
+              (const bf16*)shared, shared_stride, gate, gate_stride, (bf16*)out, out_stride, d, ids, real, (const bf16*)x, x_stride);
   else if (dtype == SI_BF16 && y_dtype == SI_BF16)
     si_launch(moe_combine_kernel<bf16, bf16>, grid, block, 0, stream, (const bf16*)Y, y_stride, place_of, wts, top,
-              (const bf16*)shared, shared_stride, gate, gate_stride, (bf16*)out, out_stride, d);
+              (const bf16*)shared, shared_stride, gate, gate_stride, (bf16*)out, out_stride, d, ids, real, (const bf16*)x, x_stride);
   else if (dtype == SI_F32 && y_dtype == SI_F32)
     si_launch(moe_combine_kernel<float, float>, grid, block, 0, stream, (const float*)Y, y_stride, place_of, wts, top,
-              (const float*)shared, shared_stride, gate, gate_stride, (float*)out, out_stride, d);
+              (const float*)shared, shared_stride, gate, gate_stride, (float*)out, out_stride, d, ids, real, (const float*)x, x_stride);
   else
     return -2;
   return si_last_error();

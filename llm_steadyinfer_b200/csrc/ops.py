@@ -938,15 +938,28 @@ def _f32v(t, name: str, n=None) -> None:
               f"{name} must be contiguous fp32" + (f" of {n} elements" if n is not None else ""))
 
 
+def _q_temp(q_temp):
+    """(coef, every) of a query temperature as the kernels take it; None: (0, 0), no temperature."""
+    if q_temp is None:
+        return 0.0, 0
+    coef, every = float(q_temp[0]), int(q_temp[1])
+    _need(every > 0 and every == q_temp[1], "query temperature: 'every' must be a positive whole number")
+    return coef, every
+
+
 def attention_general(q, k_cache, v_cache, block_table, row_seq, positions, out, page_size: int, num_seqs: int,
                       H: int, KV: int, dk: int, dv: int, scale: float, window: int = 0, dist_bias=None, sink=None,
-                      status=None, softcap: float = 0.0, v_share: int = 1) -> None:
+                      status=None, softcap: float = 0.0, v_share: int = 1, slopes=None, q_temp=None) -> None:
     """fp32-arithmetic attention over the paged cache with key size ``dk``, value size ``dv``, values from
     ``v_cache`` or (None) the first ``dv`` entries of the keys, a bias by distance ``dist_bias`` (fp32 [nd, H],
     row min(distance, nd - 1)) and a sink per head (fp32 [H]) in the softmax denominator. ``softcap`` > 0: the scaled
     score s becomes softcap * tanh(s / softcap). ``v_share`` > 1: that many neighbouring key heads read one value head
-    (``v_cache`` holds KV / v_share heads). ``out`` may be fp32 whatever the storage."""
-    _cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, dist_bias, sink, status)
+    (``v_cache`` holds KV / v_share heads). ``slopes`` (fp32 [H]): ``slopes[h] * (i - j)`` is taken off the scaled score of
+    query i and key j. ``q_temp`` ``(coef, every)``: row i's scale is multiplied by 1 + coef * ln(floor((i + 1) / every) + 1).
+    ``out`` may be fp32 whatever the storage."""
+    _cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, dist_bias, sink, slopes, status)
+    _f32v(slopes, "slopes", H)
+    qt_coef, qt_every = _q_temp(q_temp)
     _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
     T = q.shape[0]
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == H * dk and out.shape[1] == H * dv,
@@ -967,23 +980,30 @@ def attention_general(q, k_cache, v_cache, block_table, row_seq, positions, out,
     _f32v(sink, "sink", H)
     f = _fn("attention_general", "si_attention_general",
             [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_f, _c_int, _c_int, _c_p, _c_p])
+             _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_f, _c_int, _c_int, _c_p, _c_f, _c_int,
+             _c_p, _c_p])
     _check(f(_ptr(q), _dt(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(row_seq), _ptr(positions), _ptr(out), out.stride(0), k_cache.shape[0], page_size, T, num_seqs,
              H, KV, dk, dv, float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), float(softcap or 0.0),
-             int(v_share), 1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0, _ptr(status), _stream()),
+             int(v_share), 1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0, _ptr(slopes), qt_coef,
+             qt_every, _ptr(status), _stream()),
            f"attention_general(dk={dk}, dv={dv})")
 
 
 def kv_store(qkv, positions, row_seq, block_table, k_cache, v_cache, page_size: int, num_seqs: int, H: int,
              KV: int, dk: int, dv: int, status=None) -> None:
-    """Rows [q: H*dk | k: KV*dk | v: KV*dv]: k and v of every row into its page, unrotated."""
+    """Rows [q: H*dk | k: KV*dk | v: KV*dv | ...]: k and v of every row into its page, unrotated. ``v_cache`` None with
+    ``dv`` 0: the keys alone (a layer whose keys serve as its values)."""
     _cuda(qkv, positions, row_seq, block_table, k_cache, v_cache, status)
     _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
-    _need(qkv.stride(1) == 1 and qkv.shape[1] == H * dk + KV * (dk + dv), "kv_store: row layout")
-    _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
-          and tuple(k_cache.shape[1:]) == (KV, page_size, dk) and tuple(v_cache.shape) == (k_cache.shape[0], KV, page_size, dv),
-          "kv_store: caches must be [pages, KV, page_size, dk] and [pages, KV, page_size, dv]")
+    _need(qkv.stride(1) == 1 and qkv.shape[1] >= H * dk + KV * (dk + dv), "kv_store: row layout")
+    _need(k_cache.dtype == qkv.dtype and k_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (KV, page_size, dk),
+          "kv_store: keys must be [pages, KV, page_size, dk]")
+    if v_cache is None:
+        _need(dv == 0, "kv_store: without a value cache dv must be 0")
+    else:
+        _need(v_cache.dtype == qkv.dtype and v_cache.is_contiguous() and tuple(v_cache.shape) == (k_cache.shape[0], KV, page_size, dv),
+              "kv_store: values must be [pages, KV, page_size, dv]")
     f = _fn("attention_general", "si_kv_store",
             [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
              _c_int, _c_int, _c_p, _c_p])
@@ -993,13 +1013,15 @@ def kv_store(qkv, positions, row_seq, block_table, k_cache, v_cache, page_size: 
 
 
 def latent_prepare(kv, q, q_full, norm_w, eps: float, inv_freq, rot_dims: int, positions, row_seq, block_table,
-                   k_cache, page_size: int, num_seqs: int, H: int, dq: int, dr: int, rk: int, status=None, q_exp=None) -> None:
+                   k_cache, page_size: int, num_seqs: int, H: int, dq: int, dr: int, rk: int, status=None, q_exp=None,
+                   interleaved: bool = False, rot_scale: float = 1.0) -> None:
     """The latent attention's step between its projections and the attention itself. ``kv`` [T, rk + dr]: the
     latent is normalised (weight ``norm_w``) and stored with the rotated shared key part as one key of rk + dr
     entries (``k_cache`` [pages, 1, page_size, rk + dr]; None: nothing stored). ``q`` [T, H * (dq + dr)]: every head's
     last dr entries are rotated into ``q_full[:, h, rk:]`` (``q_full`` [T, H * (rk + dr)]; its first rk entries per
-    head are the caller's). The first ``rot_dims`` of the dr entries are rotated in rotate-half pairs. ``q_exp``
-    (optional, like ``q``) receives every head's [plain part | rotated part]."""
+    head are the caller's). The first ``rot_dims`` of the dr entries are rotated, in pairs (i, i + rot_dims/2) or, when
+    ``interleaved``, (2i, 2i + 1); cosines and sines are multiplied by ``rot_scale``. ``q_exp`` (optional, like ``q``)
+    receives every head's [plain part | rotated part]."""
     _cuda(kv, q, q_full, norm_w, inv_freq, positions, row_seq, block_table, k_cache, status, q_exp)
     if q_exp is not None:
         _need(q_exp.shape == q.shape and q_exp.dtype == q.dtype and q_exp.stride(1) == 1, "latent_prepare: q_exp must be like q")
@@ -1017,12 +1039,13 @@ def latent_prepare(kv, q, q_full, norm_w, eps: float, inv_freq, rot_dims: int, p
         num_pages = k_cache.shape[0]
     f = _fn("attention_general", "si_latent_prepare",
             [_c_p, _c_int, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_f, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_p,
-             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_p, _c_p])
     _check(f(_ptr(kv), _dt(kv), kv.stride(0), _ptr(q), q.stride(0), _ptr(q_full), q_full.stride(0), _ptr(q_exp),
              q_exp.stride(0) if q_exp is not None else 0, _ptr(norm_w),
              float(eps), _ptr(inv_freq), int(rot_dims), _ptr(positions), _ptr(row_seq), _ptr(block_table),
              block_table.shape[1] if block_table is not None else 0, _ptr(k_cache), num_pages, page_size, T, num_seqs,
-             H, dq, dr, rk, _ptr(status), _stream()), f"latent_prepare(rank={rk}, rot={dr})")
+             H, dq, dr, rk, 1 if interleaved else 0, float(rot_scale), _ptr(status), _stream()),
+           f"latent_prepare(rank={rk}, rot={dr})")
 
 
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
@@ -1040,6 +1063,17 @@ def activation(x, out, kind: str) -> None:
 
 
 # ---- state-space mixer ---------------------------------------------------------------------------------
+
+def sigmoid_gate(a, gate, out) -> None:
+    """out = a * sigmoid(gate) entry by entry (fp32 arithmetic): ``a`` [T, W] in fp32 or out's dtype, ``gate`` and ``out`` [T, W]
+    in the compute dtype, all rows with a stride (views into a stacked projection); ``out`` may be ``a``."""
+    _cuda(a, gate, out)
+    _need(a.dim() == 2 and gate.shape == a.shape and out.shape == a.shape and a.stride(1) == 1 and gate.stride(1) == 1
+          and out.stride(1) == 1 and gate.dtype == out.dtype and a.dtype in (out.dtype, torch.float32), "sigmoid_gate: shapes or dtypes")
+    f = _fn("activation", "si_sigmoid_gate", [_c_p, _c_int, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(a), 1 if a.dtype == torch.float32 and out.dtype != torch.float32 else 0, a.stride(0), _ptr(gate), gate.stride(0),
+             _ptr(out), out.stride(0), _dt(out), a.shape[0], a.shape[1], _stream()), "sigmoid_gate")
+
 
 def causal_conv(u, weight, bias, state, conv_off: int, out, positions, row_seq, q_start, ctx_len, slots,
                 num_seqs: int, status=None) -> None:
@@ -1149,14 +1183,16 @@ def attn_flex_scratch_floats(num_items: int, H: int, KV: int, dv: int, nsplit: i
 
 def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int, dk: int,
               dv: int, scale: float, window: int = 0, dist_bias=None, sink=None, nsplit: int = 1, scratch=None,
-              status=None, max_rows: int = 0, softcap: float = 0.0, v_share: int = 1) -> None:
+              status=None, max_rows: int = 0, softcap: float = 0.0, v_share: int = 1, slopes=None, q_temp=None) -> None:
     """``attention_general`` on the tensor cores for bfloat16. ``items``: int32 [n, 4] rows (sequence, first row,
     tokens, first position) of at most ``attn_flex_tokens`` tokens. ``nsplit`` > 1 cuts every item's keys into that
     many shares (decode rows over long contexts); ``scratch`` then holds ``attn_flex_scratch_floats`` floats.
     ``max_rows``: the most rows (tokens x query heads of a key head served together) of any item when the caller knows it
     (0: unknown); at most 16 rows over keys that are their own values let a block's warps take a value slice each.
-    ``softcap``, ``v_share`` as in ``attention_general``; ``out`` may be fp32."""
-    _cuda(q, k_cache, v_cache, block_table, items, out, dist_bias, sink, scratch, status)
+    ``softcap``, ``v_share``, ``slopes``, ``q_temp`` as in ``attention_general``; ``out`` may be fp32."""
+    _cuda(q, k_cache, v_cache, block_table, items, out, dist_bias, sink, scratch, slopes, status)
+    _f32v(slopes, "slopes", H)
+    qt_coef, qt_every = _q_temp(q_temp)
     _i32(block_table, "block_table"); _i32(items, "items")
     _need(v_share >= 1 and KV % v_share == 0 and (v_share == 1 or v_cache is not None), "attn_flex: v_share")
     _need(q.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32) and k_cache.dtype == torch.bfloat16
@@ -1183,11 +1219,13 @@ def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_
               f"attn_flex: scratch must hold {need} floats")
     f = _fn("attention_flex", "si_attn_flex",
             [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p])
+             _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_f, _c_int, _c_int, _c_p, _c_f, _c_int,
+             _c_p, _c_p])
     _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(items),
              items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs, H, KV, dk, dv,
              float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), int(nsplit), _ptr(scratch), int(max_rows),
-             float(softcap or 0.0), int(v_share), 1 if out.dtype == torch.float32 else 0, _ptr(status), _stream()), f"attn_flex(heads={H}, kv_heads={KV}, dk={dk}, dv={dv})", kernels=2 if nsplit > 1 else 1)
+             float(softcap or 0.0), int(v_share), 1 if out.dtype == torch.float32 else 0, _ptr(slopes), qt_coef, qt_every,
+             _ptr(status), _stream()), f"attn_flex(heads={H}, kv_heads={KV}, dk={dk}, dv={dv})", kernels=2 if nsplit > 1 else 1)
 
 
 # ---- one small matrix per head (decode rows) -----------------------------------------------------------------
@@ -1507,16 +1545,19 @@ def glu_limited(gu, bias, out, group, limit: float, alpha: float) -> None:
 
 # ---- routed feed-forward (mixture of experts) ----------------------------------------------------------------------------
 
-MOE_ACTS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3}
+MOE_ACTS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3, "glu_limited": 4}
 MOE_SCORES = {"sigmoid": 0, "softmax": 1}
 
 
-def moe_route(x, w, E: int, top: int, scale: float, ids, wts, gates=None, scores: str = "sigmoid", renorm: bool = False) -> None:
+def moe_route(x, w, E: int, top: int, scale: float, ids, wts, gates=None, scores: str = "sigmoid", renorm: bool = False,
+              choice_bias=None) -> None:
     """Scores of ``E`` experts for every row and the ``top`` largest: ``w`` [E + extra, d] holds the router's rows and
     behind them ``extra`` gate rows; ``ids`` int32 [T, top], ``wts`` fp32 [T, top] = score * scale (``renorm``: divided by
     the chosen scores' sum first), ``gates`` fp32 [T, extra] = sigmoid(w_gate . x). Scores are sigmoid(z) or softmax(z) of
-    z = w x, summed in fp32 whatever the storage."""
-    _cuda(x, w, ids, wts, gates)
+    z = w x, summed in fp32 whatever the storage. ``choice_bias`` (fp32 [E]): the ``top`` largest of score + bias are chosen;
+    the weights are still made of the scores alone."""
+    _cuda(x, w, ids, wts, gates, choice_bias)
+    _f32v(choice_bias, "choice_bias", E)
     T, d = x.shape
     extra = w.shape[0] - E
     _need(x.stride(1) == 1 and w.is_contiguous() and w.shape[1] == d and w.dtype == x.dtype and extra >= 0, "moe_route: x [T, d], w [E + extra, d]")
@@ -1527,9 +1568,9 @@ def moe_route(x, w, E: int, top: int, scale: float, ids, wts, gates=None, scores
         _need(gates is not None and gates.dtype == torch.float32 and gates.is_contiguous() and gates.shape == (T, extra),
               "moe_route: gates must be fp32 [T, extra]")
     f = _fn("moe", "si_moe_route", [_c_p, _c_int, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p,
-                                    _c_p, _c_int, _c_p])
+                                    _c_p, _c_p, _c_int, _c_p])
     _check(f(_ptr(x), _dt(x), x.stride(0), _ptr(w), E, extra, d, top, float(scale), MOE_SCORES[scores], 1 if renorm else 0,
-             _ptr(ids), _ptr(wts), _ptr(gates), T, _stream()), f"moe_route(experts={E}, top={top})")
+             _ptr(choice_bias), _ptr(ids), _ptr(wts), _ptr(gates), T, _stream()), f"moe_route(experts={E}, top={top})")
 
 
 MOE_PLAN_CHUNK = 1024
@@ -1588,7 +1629,7 @@ def moe_gemm_tc05(a, w, out, offsets, act: str = "none", status=None) -> None:
     _i32(offsets, "offsets")
     E, N, K = w.shape
     P = out.shape[0]
-    _need(a.shape == (P, K) and a.stride(1) == 1 and out.shape == (P, N) and out.stride(1) == 1 and offsets.numel() == E + 1,
+    _need(a.shape == (P, K) and a.stride(1) == 1 and out.shape == (P, N) and out.stride(1) == 1 and offsets.numel() >= E + 1,
           "moe_gemm_tc05: a [P, K], w [E, N, K], out [P, N]")
     _need(moe_gemm_grouped_ok(a, w, out, P, act), "moe_gemm_tc05: bf16, at least 128 places, K a multiple of 8, aligned rows")
     f = _fn("gemm_tc05", "si_gemm_tc05_grouped", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int,
@@ -1597,7 +1638,7 @@ def moe_gemm_tc05(a, w, out, offsets, act: str = "none", status=None) -> None:
              _GROUPED_TC05_ACTS[act], _ptr(status), _stream()), f"moe_gemm_tc05(experts={E}, N={N}, K={K})")
 
 
-def moe_gemm_tiles(a, a_rows, w, out, offsets, act: str = "none") -> None:
+def moe_gemm_tiles(a, a_rows, w, out, offsets, act: str = "none", limit: float = 0.0, alpha: float = 1.702) -> None:
     """``moe_gemm`` on the mma.sync tiles (bf16) or in true 32-bit, whatever the number of places."""
     _cuda(a, a_rows, w, out, offsets)
     _i32(a_rows, "a_rows"); _i32(offsets, "offsets")
@@ -1605,18 +1646,25 @@ def moe_gemm_tiles(a, a_rows, w, out, offsets, act: str = "none") -> None:
     E, N, K = w.shape
     P = out.shape[0]
     _need(a.dim() == 2 and a.shape[1] == K and a.stride(1) == 1 and w.is_contiguous() and w.dtype == a.dtype, "moe_gemm: a [*, K], w [E, N, K]")
-    _need(out.shape == (P, N) and out.stride(1) == 1 and out.dtype in (a.dtype, torch.float32), "moe_gemm: out must be [P, N]")
-    _need(offsets.numel() == E + 1 and (a_rows is None or a_rows.numel() == P) and (a_rows is not None or a.shape[0] >= P), "moe_gemm: sizes")
-    f = _fn("moe", "si_moe_gemm", [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    pair = act == "glu_limited"                       # gate and up rows in turn: an entry of the result for every two rows
+    _need(not pair or (N % 2 == 0 and limit > 0), "moe_gemm: glu_limited needs an even N and a positive limit")
+    _need(out.shape == (P, N // 2 if pair else N) and out.stride(1) == 1 and out.dtype in (a.dtype, torch.float32),
+          "moe_gemm: out must be [P, N] (glu_limited: [P, N / 2])")
+    _need(offsets.numel() >= E + 1 and (a_rows is None or a_rows.numel() == P) and (a_rows is not None or a.shape[0] >= P), "moe_gemm: sizes")
+    f = _fn("moe", "si_moe_gemm", [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                   _c_f, _c_f, _c_p])
     _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(a_rows), _ptr(w), _ptr(out), _dt(out), out.stride(0), _ptr(offsets), P, E, N, K,
-             MOE_ACTS[act], _stream()), f"moe_gemm(experts={E}, N={N}, K={K})")
+             MOE_ACTS[act], float(limit), float(alpha), _stream()), f"moe_gemm(experts={E}, N={N}, K={K})")
 
 
-def moe_gemm(a, a_rows, w, out, offsets, act: str = "none", gathered=None, status=None) -> None:
+def moe_gemm(a, a_rows, w, out, offsets, act: str = "none", gathered=None, status=None, limit: float = 0.0,
+             alpha: float = 1.702) -> None:
     """out[p, :] = act(a[row(p), :] @ w[e]^T) for every place p of expert e (``offsets`` int32 [E + 1] as ``moe_plan``
     leaves them); row(p) = a_rows[p] (int32 [P]) or p itself (None). ``a`` [*, K] and ``w`` [E, N, K] of one dtype;
     ``out`` [P, N] in that dtype or fp32. bf16 on the tensor cores with fp32 sums (tcgen05 where ``moe_gemm_grouped_ok``;
-    a product that gathers then copies its rows into ``gathered`` [P, K] first), fp32 in true 32-bit."""
+    a product that gathers then copies its rows into ``gathered`` [P, K] first), fp32 in true 32-bit. ``offsets`` may hold
+    more entries than E + 1 (experts behind the E that have weights, which get no product); places behind offsets[E] are
+    left alone. act "glu_limited": ``w`` holds gate and up rows in turn and ``out`` is [P, N / 2] (``limit``, ``alpha``)."""
     P = out.shape[0]
     if moe_gemm_grouped_ok(a, w, out, P, act) and (a_rows is None or gathered is not None):
         if a_rows is not None:
@@ -1624,14 +1672,19 @@ def moe_gemm(a, a_rows, w, out, offsets, act: str = "none", gathered=None, statu
             a = gathered
         moe_gemm_tc05(a[:P], w, out, offsets, act, status)
     else:
-        moe_gemm_tiles(a, a_rows, w, out, offsets, act)
+        moe_gemm_tiles(a, a_rows, w, out, offsets, act, limit, alpha)
 
 
-def moe_combine(y, place_of, wts, out, shared=None, gate=None) -> None:
+def moe_combine(y, place_of, wts, out, shared=None, gate=None, ids=None, real: int = 0, x=None) -> None:
     """out[t, :] = sum_c wts[t, c] * y[place_of[t, c], :] (+ gate[t] * shared[t, :]): ``y`` [P, d] (fp32 or out's dtype),
     ``place_of`` int32 [T, top], ``wts`` fp32 [T, top], ``shared`` [T, d] in out's dtype or None, ``gate`` fp32 [T] (a strided
-    view; None: 1), ``out`` [T, d]."""
-    _cuda(y, place_of, wts, out, shared, gate)
+    view; None: 1), ``out`` [T, d]. With ``ids`` (int32 [T, top]) a choice whose id is ``real`` or above is an identity expert:
+    its result is the row ``x[t]`` itself (``x`` [T, d] in out's dtype) and ``y`` is not read there."""
+    _cuda(y, place_of, wts, out, shared, gate, ids, x)
+    if ids is not None:
+        _i32(ids, "ids")
+        _need(ids.shape == tuple(place_of.shape) and ids.is_contiguous() and x is not None and x.shape == tuple(out.shape)
+              and x.stride(1) == 1 and x.dtype == out.dtype, "moe_combine: ids [T, top] with x [T, d]")
     _i32(place_of, "place_of")
     T, d = out.shape
     top = wts.shape[1]
@@ -1641,9 +1694,12 @@ def moe_combine(y, place_of, wts, out, shared=None, gate=None) -> None:
         _need(shared.shape == (T, d) and shared.stride(1) == 1 and shared.dtype == out.dtype, "moe_combine: shared must be [T, d]")
     if gate is not None:
         _need(shared is not None and gate.dtype == torch.float32 and gate.dim() == 1 and gate.shape[0] == T, "moe_combine: gate must be fp32 [T]")
-    f = _fn("moe", "si_moe_combine", [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_int, _c_p, _c_ll, _c_p, _c_int, _c_p, _c_int, _c_ll, _c_int, _c_int, _c_p])
+    f = _fn("moe", "si_moe_combine", [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_int, _c_p, _c_ll, _c_p, _c_int, _c_p, _c_int, _c_ll, _c_int, _c_int,
+                                      _c_p, _c_int, _c_p, _c_ll, _c_p])
     _check(f(_ptr(y), _dt(y), y.stride(0), _ptr(place_of), _ptr(wts), top, _ptr(shared), shared.stride(0) if shared is not None else 0,
-             _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), _dt(out), out.stride(0), T, d, _stream()),
+             _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), _dt(out), out.stride(0), T, d,
+             _ptr(ids) if ids is not None else None, int(real), _ptr(x) if ids is not None else None,
+             x.stride(0) if ids is not None else 0, _stream()),
            f"moe_combine(d={d})")
 
 

@@ -1,2 +1,2 @@
-from . import llama, mivorax, nufasun, vibunex  # noqa: F401  (register "LlamaForCausalLM", "Mivorax", "Nufasun", "Vibunex")
+from . import fevosun, llama, mivorax, nufasun, vibunex  # noqa: F401  (register "Fevosun", "LlamaForCausalLM", "Mivorax", "Nufasun", "Vibunex")
 from .model import Model

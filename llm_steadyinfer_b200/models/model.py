@@ -37,7 +37,8 @@ class Model:
             ffn = n2 = None
             if ls.feed_forward is not None:
                 ffn = feed_forward_class(ls.feed_forward.kind)(ls.feed_forward.params, dtype, self.device)
-                n2 = norm_class(ls.feed_forward_norm.kind)(ls.feed_forward_norm.params, dtype, self.device)
+                if ls.feed_forward_norm is not None:      # None: the feed-forward reads the mixer's norm (an arrangement's choice)
+                    n2 = norm_class(ls.feed_forward_norm.kind)(ls.feed_forward_norm.params, dtype, self.device)
             n1 = norm_class(ls.mixer_norm.kind)(ls.mixer_norm.params, dtype, self.device)
             n1b = n2b = None                          # norms behind the sublayers, where the layer has them
             if ls.mixer_post_norm is not None:
@@ -86,7 +87,8 @@ class Model:
                 yield p + ls.feed_forward_gate_name, b.feed_forward_gate
             if b.feed_forward is not None:
                 yield p + ls.feed_forward_prefix, b.feed_forward
-                yield p + ls.feed_forward_norm_name, b.feed_forward_norm
+                if b.feed_forward_norm is not None:
+                    yield p + ls.feed_forward_norm_name, b.feed_forward_norm
                 if b.feed_forward_post_norm is not None:
                     yield p + ls.feed_forward_post_norm_name, b.feed_forward_post_norm
         yield self.spec.final_norm_name, self.final_norm

@@ -16,7 +16,15 @@ Options beyond the reference's block, all parameters of the part:
                    checkpoint's tensor says how many rows there are. At load the table is spread out by distance
                    (one row for every n up to D), which is what the kernels index.
 ``names``          checkpoint names of the four matrices, ``{"q": .., "k": .., "v": .., "o": ..}``.
-With either of the first two the mixer runs the general attention kernels (``attention_general.cu`` in 32-bit,
+``values_are_keys`` the layer has no value projection: head g's value at a position is its key there, so the cache keeps keys
+                   alone and the kernels read the values out of the key pages (a ``value_dim`` below ``head_dim``: the key's first entries).
+``distance_slopes`` ``{"base": b, "exponent": e}``: ``slope_h * (i - j)`` with ``slope_h = b^(e (h + 1) / heads)`` is taken off
+                   the scaled score of query i and key j (a penalty in proportion to the distance, steeper for the first heads).
+``query_temperature`` ``{"coef": c, "every": n}``: the query at position p is multiplied by ``1 + c ln(floor((p + 1) / n) + 1)``
+                   (applied by the attention kernels to the row's scale, in fp32).
+``output_gate``    name of a matrix [heads * value_dim, hidden]: the heads' results are multiplied entry by entry with
+                   ``sigmoid(W_g x)`` before the output projection; its rows are stacked behind q, k, v in one product.
+With any option but ``names`` the mixer runs the general attention kernels (``attention_general.cu`` in 32-bit,
 ``attention_flex.cu`` on the tensor cores in bfloat16) instead of the rotary ones.
 """
 from __future__ import annotations
@@ -65,9 +73,27 @@ class Attention(Mixer):
             self.bias_name = self.bias_spec.get("name", "distance_bias")
             self.bias_rows = self.bias_spec.get("buckets")
             self.bias_max = float(self.bias_spec["max_distance"])
-        self.general = self.bias_spec is not None or self.vs != self.hs
+        self.own_v = not bool(params.get("values_are_keys", False))
+        if not self.own_v and self.vs > self.hs:
+            raise ValueError(f"attention: values that are the keys have at most the keys' size {self.hs}, found value_dim {self.vs}")
+        sl = params.get("distance_slopes") or None
+        self.slopes = None               # fp32 [H] on the device
+        if sl is not None:
+            base, expo = float(sl["base"]), float(sl["exponent"])
+            self.slopes = torch.tensor([base ** (expo * (h + 1) / self.H) for h in range(self.H)], dtype=torch.float64) \
+                .to(torch.float32).to(device)
+        qt = params.get("query_temperature") or None
+        self.q_temp = None if qt is None else (float(qt["coef"]), qt["every"])
+        self.gate_name = params.get("output_gate") or None
+        self.general = (self.bias_spec is not None or self.vs != self.hs or not self.own_v or self.slopes is not None
+                        or self.q_temp is not None or self.gate_name is not None)
         if self.general and position is not None:
-            raise ValueError("attention: a distance bias or a value size of its own goes without a position encoding")
+            raise ValueError("attention: the general form (a distance bias, slopes, a value size of its own, values that are "
+                             "the keys, a query temperature, an output gate) goes without a position encoding")
+        # columns of the stacked projection: q, k, v (if the layer has values of its own), the gate (if it has one)
+        self.kv_cols = self.KV * (self.hs + (self.vs if self.own_v else 0))
+        self.gate_off = self.H * self.hs + self.kv_cols
+        self.proj_cols = -(-(self.gate_off + (self.H * self.vs if self.gate_name else 0)) // 8) * 8 if self.general else 0
         self.dist_bias = None            # fp32 [distances, H], made at load
         self.qkv = None
         self.o = None
@@ -76,8 +102,11 @@ class Attention(Mixer):
         n = self.names
         shapes = {n["q"]: (self.H * self.hs, self.hidden),
                   n["k"]: (self.KV * self.hs, self.hidden),
-                  n["v"]: (self.KV * self.vs, self.hidden),
                   n["o"]: (self.hidden, self.H * self.vs)}
+        if self.own_v:
+            shapes[n["v"]] = (self.KV * self.vs, self.hidden)
+        if self.gate_name:
+            shapes[self.gate_name] = (self.H * self.vs, self.hidden)
         if self.bias_spec is not None:
             shapes[self.bias_name] = (self.bias_rows if self.bias_rows else -1, self.H)   # -1: as the checkpoint has it
         return shapes
@@ -90,12 +119,19 @@ class Attention(Mixer):
 
     def load_weights(self, tensors):
         n = self.names
-        self.qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], 0).contiguous()
+        parts = [tensors[n["q"]], tensors[n["k"]]] + ([tensors[n["v"]]] if self.own_v else []) \
+            + ([tensors[self.gate_name]] if self.gate_name else [])
+        rows = sum(p.shape[0] for p in parts)
+        if self.general and rows < self.proj_cols:           # rows of the product's result stay 16-byte aligned
+            parts.append(torch.zeros(self.proj_cols - rows, self.hidden, dtype=parts[0].dtype, device=parts[0].device))
+        self.qkv = torch.cat(parts, 0).contiguous()
         self.o = tensors[n["o"]].contiguous()
         if self.bias_spec is not None:
             self.dist_bias = spread_by_distance(tensors[self.bias_name].float(), self.bias_max)
 
     def cache_need(self):
+        if not self.own_v:
+            return CacheNeed(self.KV, self.hs, self.window, 0)
         return CacheNeed(self.KV, self.hs, self.window, None if self.vs == self.hs else self.vs)
 
     @property
@@ -110,8 +146,8 @@ class Attention(Mixer):
 
     def kernel_files(self, page_size):
         if self.general:
-            return ("attention_general",) + (("gemm_f32",) if self.dtype == torch.float32
-                                             else ("attention_flex", "gemm_skinny", "gemm_rows", "gemm_tc05"))
+            return ("attention_general",) + (("activation",) if self.gate_name else ()) + (
+                ("gemm_f32",) if self.dtype == torch.float32 else ("attention_flex", "gemm_skinny", "gemm_rows", "gemm_tc05"))
         names = ["rope_kv"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_skinny", "gemm_rows", "gemm_tc05"])
         if not self.uses_tensor_cores():
             return tuple(names + ["attention_ref"])
@@ -156,23 +192,27 @@ class Attention(Mixer):
         return out
 
     def forward_general(self, x, ctx, cache):
-        """No rotation; keys and values of their own sizes into the pages as they are; scores with the bias."""
+        """No rotation; keys (and values of their own size, where the layer has them) into the pages as they are; scores with
+        the bias, the slopes and the query temperature; the gate on the heads' results."""
         T = x.shape[0]
         H, KV, hs, vs = self.H, self.KV, self.hs, self.vs
-        qkv = ctx.buf("attn_qkv", (T, H * hs + KV * (hs + vs)), self.dtype)
+        qkv = ctx.buf("attn_qkv", (T, self.proj_cols), self.dtype)
         linear(x, self.qkv, qkv, ctx.status)
+        v_cache = cache.v if self.own_v else None
         if cache.writes:
-            ops.kv_store(qkv, ctx.positions, ctx.row_seq, cache.block_table, cache.k, cache.v, cache.page_size,
-                         ctx.seq_slots, H, KV, hs, vs, status=ctx.status)
+            ops.kv_store(qkv, ctx.positions, ctx.row_seq, cache.block_table, cache.k, v_cache, cache.page_size,
+                         ctx.seq_slots, H, KV, hs, vs if self.own_v else 0, status=ctx.status)
         attn = ctx.buf("attn_out", (T, H * vs), self.dtype)
         if self.uses_flex():
-            flex_plan.attend(flex_plan.plan(ctx, self.device, H, KV, hs, vs, True, self.window), qkv[:, :H * hs], cache.k,
-                             cache.v, cache.block_table, attn, cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale,
-                             self.window, dist_bias=self.dist_bias, status=ctx.status)
+            flex_plan.attend(flex_plan.plan(ctx, self.device, H, KV, hs, vs, self.own_v, self.window), qkv[:, :H * hs], cache.k,
+                             v_cache, cache.block_table, attn, cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale,
+                             self.window, dist_bias=self.dist_bias, status=ctx.status, slopes=self.slopes, q_temp=self.q_temp)
         else:
-            ops.attention_general(qkv[:, :H * hs], cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.positions, attn,
+            ops.attention_general(qkv[:, :H * hs], cache.k, v_cache, cache.block_table, ctx.row_seq, ctx.positions, attn,
                                   cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale, self.window or 0,
-                                  dist_bias=self.dist_bias, status=ctx.status)
+                                  dist_bias=self.dist_bias, status=ctx.status, slopes=self.slopes, q_temp=self.q_temp)
+        if self.gate_name:
+            ops.sigmoid_gate(attn, qkv[:, self.gate_off:self.gate_off + H * vs], attn)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(attn, self.o, out, ctx.status)
         return out
@@ -185,7 +225,7 @@ class Attention(Mixer):
     def uses_flex(self) -> bool:
         """The general form on the tensor cores: bfloat16 and sizes in multiples of 8."""
         return (self.general and self.dtype == torch.bfloat16 and USE_TENSOR_CORES
-                and ops.attn_flex_ok(self.H, self.KV, self.hs, self.vs, True))
+                and ops.attn_flex_ok(self.H, self.KV, self.hs, self.vs, self.own_v))
 
     def uses_tensor_cores(self) -> bool:
         return not self.general and self.dtype == torch.bfloat16 and USE_TENSOR_CORES and self.hs % 16 == 0
@@ -196,7 +236,7 @@ class Attention(Mixer):
         kernel's item size. One plan serves every layer with the same head layout and window."""
         if self.general:
             if self.uses_flex() and cache.k is not None:
-                flex_plan.plan(ctx, self.device, self.H, self.KV, self.hs, self.vs, True, self.window)
+                flex_plan.plan(ctx, self.device, self.H, self.KV, self.hs, self.vs, self.own_v, self.window)
             return
         if not self.uses_tensor_cores():
             return

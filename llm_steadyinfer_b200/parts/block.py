@@ -17,6 +17,10 @@ norm's launch normalises and adds before its own statistics (no launch of its ow
 a learned gate (``SublayerGate``: sigmoid of a projection of the sublayer's own input plus a bias, entry by entry):
     h += delta_in;  x1 = norm1(h);  x2 = norm2(h);  h += scale * (gate1(x1) * mixer(x1) + gate2(x2) * ffn(x2))
 The add is one kernel in fp32 on the stream itself (``ops.gated_add``), so the block hands no pending delta on.
+"parallel" runs both sublayers on the output of one norm and adds both results to the stream:
+    h += delta_in;  x = norm1(h);  h += mixer(x);  return ffn(x), still to be added
+(the mixer's result joins the fp32 stream at once, in a launch of its own, so that the feed-forward may use the same scratch;
+the feed-forward's is the pending delta of the next norm, as in "pre_norm").
 Another arrangement (post-norm, ...) is added with ``register_arrangement`` and needs no change here.
 """
 from __future__ import annotations
@@ -152,6 +156,20 @@ def sandwich(block: Block, resid, delta, ctx, cache):
 
 
 register_arrangement("sandwich", sandwich, capturable=True)
+
+
+def parallel(block: Block, resid, delta, ctx, cache):
+    T, d = resid.shape
+    x = ctx.buf("block_x", (T, d), block.mixer.dtype)
+    block.norm(block.mixer_norm, resid, delta, x, block.mixer.streams_first(T))
+    a = block.mixer.forward(x, ctx, cache)
+    if block.feed_forward is None:
+        return a
+    ops.add_norm(resid, a)                                # fp32 sum; ``x`` is untouched and feeds the second sublayer
+    return block.feed_forward.forward(x, ctx)
+
+
+register_arrangement("parallel", parallel, capturable=True)
 
 
 def parallel_gated(block: Block, resid, delta, ctx, cache):

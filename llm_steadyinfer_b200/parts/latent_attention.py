@@ -21,9 +21,16 @@ into per-head keys [W_uk,i c | k_rot] and values W_uv,i c, and ordinary multi-he
 them with the whole queries. Which sequences of a step go which way is decided on the host in ``prepare`` (those
 that bring at least ``EXPAND_MIN_ROWS`` rows); both ways compute the same function, up to rounding.
 
-Tensor names below the part's prefix: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, sink, o.
+Options: ``q_rank`` None: the queries have no latent, q = W_q h (tensor ``q`` instead of dq, dq.norm, uq; its rows are stacked
+on the key/value down-projection's, one product); ``q_rank`` "checkpoint": the query latent's size is that of the stored tensors; ``rot_scaling`` (a scaling rule of the rotary frequencies as ``parts/rotary.py``
+takes it; the "yarn" rule also multiplies cosines and sines by its magnitude); ``rot_interleaved`` (pairs (2i, 2i + 1) instead of
+(i, i + rot_dims / 2)); ``sink`` False; ``window``.
+
+Tensor names below the part's prefix: dq, dq.norm, uq (or q), dkv, dkv.norm, uk, uv, sink, o.
 """
 from __future__ import annotations
+
+import math
 
 import numpy as np
 import torch
@@ -51,7 +58,8 @@ class LatentAttention(Mixer):
         self.dr = int(g["rot_dim"])              # rotated part
         self.dv = int(g["value_dim"])
         self.rk = int(g["kv_rank"])
-        self.q_rank = int(g["q_rank"])
+        self.q_latent = bool(g.get("q_rank"))                            # False: queries straight from the input
+        self.q_rank = (-1 if g["q_rank"] == "checkpoint" else int(g["q_rank"])) if self.q_latent else None
         self.scale = float(g["scale"])
         self.eps = float(g["eps"])
         self.rot_dims = int(g.get("rot_dims", self.dr))       # how many of the dr entries are rotated
@@ -61,18 +69,25 @@ class LatentAttention(Mixer):
             raise ValueError(f"latent_attention: rot_dims {self.rot_dims} must be even and at most rot_dim {self.dr}")
         if self.rk + self.dr > 640:
             raise ValueError(f"latent_attention: kv_rank + rot_dim {self.rk + self.dr} above 640 is not supported")
-        self.inv_freq = rotary_inverse_frequencies(self.rot_dims, float(g["rot_base"]), None).to(device) \
+        scaling = g.get("rot_scaling") or None
+        self.interleaved = bool(g.get("rot_interleaved", False))
+        self.inv_freq = rotary_inverse_frequencies(self.rot_dims, float(g["rot_base"]), scaling).to(device) \
             if self.rot_dims else torch.zeros(0, dtype=torch.float32, device=device)
+        # what cosines and sines are multiplied by (the "yarn" rule)
+        self.rot_scale = 0.1 * math.log(float(scaling["factor"])) + 1.0 if scaling and scaling.get("rope_type") == "yarn" else 1.0
+        self.q_cols = self.q_rank if self.q_latent else self.H * (self.dq + self.dr)  # what the first product holds before [latent | key part]
         self.down = self.uq = self.ukT = self.uv = self.o = None
         self.q_norm = self.kv_norm = self.sink = None
 
     def weight_shapes(self):
         H = self.H
-        shapes = {"dq": (self.q_rank, self.hidden), "dq.norm": (self.q_rank,),
-                  "uq": (H * (self.dq + self.dr), self.q_rank),
-                  "dkv": (self.rk + self.dr, self.hidden), "dkv.norm": (self.rk,),
+        shapes = {"dkv": (self.rk + self.dr, self.hidden), "dkv.norm": (self.rk,),
                   "uk": (H * self.dq, self.rk), "uv": (H * self.dv, self.rk),
                   "o": (self.hidden, H * self.dv)}
+        if self.q_rank:
+            shapes.update({"dq": (self.q_rank, self.hidden), "dq.norm": (self.q_rank,), "uq": (H * (self.dq + self.dr), self.q_rank)})
+        else:
+            shapes["q"] = (H * (self.dq + self.dr), self.hidden)
         if self.has_sink:
             shapes["sink"] = (H,)
         return shapes
@@ -85,14 +100,16 @@ class LatentAttention(Mixer):
 
     def load_weights(self, t):
         H = self.H
-        self.down = torch.cat([t["dq"], t["dkv"]], 0).contiguous()          # one product for both latents
-        self.uq = t["uq"].contiguous()
+        if self.q_latent:
+            self.q_rank = self.q_cols = int(t["dq"].shape[0])
+        self.down = torch.cat([t["dq"] if self.q_rank else t["q"], t["dkv"]], 0).contiguous()   # one product for both
+        self.uq = t["uq"].contiguous() if self.q_rank else None
         # per head the key up-projection transposed, [rk, dq]: q_lat = q_plain @ W_uk,i as a product with rows of W^T
         self.ukT = t["uk"].view(H, self.dq, self.rk).transpose(1, 2).contiguous()
         self.uk = t["uk"].contiguous()                                        # as stored, for the expanded way
         self.uv = t["uv"].view(H, self.dv, self.rk).contiguous()
         self.o = t["o"].contiguous()
-        self.q_norm = t["dq.norm"].contiguous()
+        self.q_norm = t["dq.norm"].contiguous() if self.q_rank else None
         self.kv_norm = t["dkv.norm"].float().contiguous()
         self.sink = t["sink"].float().contiguous() if self.has_sink else None
 
@@ -156,12 +173,15 @@ class LatentAttention(Mixer):
     def forward(self, x, ctx, cache):
         T = x.shape[0]
         H, dq, dr, dv, rk = self.H, self.dq, self.dr, self.dv, self.rk
-        lat = ctx.buf("lat_down", (T, self.q_rank + rk + dr), self.dtype)
+        lat = ctx.buf("lat_down", (T, self.q_cols + rk + dr), self.dtype)
         linear(x, self.down, lat, ctx.status)
-        cq = ctx.buf("lat_cq", (T, self.q_rank), self.dtype)
-        ops.rmsnorm_rows(lat[:, :self.q_rank], self.q_norm, self.eps, cq)
-        q = ctx.buf("lat_q", (T, H * (dq + dr)), self.dtype)
-        linear(cq, self.uq, q, ctx.status)
+        if self.q_rank:
+            cq = ctx.buf("lat_cq", (T, self.q_rank), self.dtype)
+            ops.rmsnorm_rows(lat[:, :self.q_rank], self.q_norm, self.eps, cq)
+            q = ctx.buf("lat_q", (T, H * (dq + dr)), self.dtype)
+            linear(cq, self.uq, q, ctx.status)
+        else:
+            q = lat[:, :self.q_cols]
         ex = ctx.plans.get(("latent_expand", H, dq, dr, dv, rk, self.window)) if self.uses_flex() else None
         expanded = ex is not None and ex["total"] > 0
         absorbed = not (expanded and ex["all"])
@@ -175,9 +195,10 @@ class LatentAttention(Mixer):
         else:
             for i in range(H):
                 linear(q[:, i * (dq + dr): i * (dq + dr) + dq], self.ukT[i], q_full[:, i * (rk + dr): i * (rk + dr) + rk], ctx.status)
-        ops.latent_prepare(lat[:, self.q_rank:], q, q_full, self.kv_norm, self.eps, self.inv_freq, self.rot_dims,
+        ops.latent_prepare(lat[:, self.q_cols:], q, q_full, self.kv_norm, self.eps, self.inv_freq, self.rot_dims,
                            ctx.positions, ctx.row_seq, cache.block_table, cache.k if cache.writes else None,
-                           cache.page_size, ctx.seq_slots, H, dq, dr, rk, status=ctx.status, q_exp=q_exp)
+                           cache.page_size, ctx.seq_slots, H, dq, dr, rk, status=ctx.status, q_exp=q_exp,
+                           interleaved=self.interleaved, rot_scale=self.rot_scale)
         attn = ctx.buf("attn_out", (T, H * dv), self.dtype)
         if absorbed:
             self._attend_absorbed(q_full, attn, ctx, cache, ex["skip"] if expanded else frozenset())

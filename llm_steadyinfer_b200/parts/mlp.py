@@ -31,21 +31,22 @@ class GatedMLP(FeedForward):
         self.inter = int(params["intermediate_size"])
         if params.get("activation", "silu") != "silu":
             raise ValueError(f"gated_mlp: activation {params['activation']!r} is not supported")
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(params.get("names") or {})       # checkpoint names of the three matrices
         self.group = INTERLEAVE if self.inter % INTERLEAVE == 0 else self.inter
         self.gate_up = None
         self.down = None
 
     def weight_shapes(self):
-        return {"gate_proj.weight": (self.inter, self.hidden),
-                "up_proj.weight": (self.inter, self.hidden),
-                "down_proj.weight": (self.hidden, self.inter)}
+        n = self.names
+        return {n["gate"]: (self.inter, self.hidden), n["up"]: (self.inter, self.hidden), n["down"]: (self.hidden, self.inter)}
 
     def load_weights(self, tensors):
-        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        gate, up = tensors[self.names["gate"]], tensors[self.names["up"]]
         n = self.inter // self.group
         self.gate_up = torch.stack([gate.view(n, self.group, self.hidden), up.view(n, self.group, self.hidden)], 1) \
             .reshape(2 * self.inter, self.hidden).contiguous()
-        self.down = tensors["down_proj.weight"].contiguous()
+        self.down = tensors[self.names["down"]].contiguous()
 
     def streams_first(self, rows):
         # few rows in bfloat16 go to the weight-streaming product, which reads every weight once
@@ -138,7 +139,8 @@ class LimitedGatedMLP(FeedForward):
         g = min(W_gate x + b_gate, limit);  u = clamp(W_up x + b_up, -limit, limit)
         y = g * sigmoid(alpha * g) * (u + 1);  out = W_down y + b_down
     ``limit`` and ``alpha`` (default 1.702, which makes g * sigmoid(alpha g) close to gelu) are parameters; so are the
-    tensor names (``names``: gate, up, down; each bias is the matrix's name + ``bias_suffix``). gate and up are
+    tensor names (``names``: gate, up, down; each bias is the matrix's name + ``bias_suffix``; ``biases`` False: the
+    checkpoint has none and they count as zero). gate and up are
     stacked and interleaved as in ``GatedMLP``, and as there the activation (biases and limits included) runs in the
     epilogue of the first product for decode rows and for prompt portions in bfloat16; elsewhere a kernel of its own
     applies it to the stored product. Either way it is fp32 arithmetic on the product rounded to the compute dtype.
@@ -157,16 +159,19 @@ class LimitedGatedMLP(FeedForward):
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
         self.names.update(params.get("names") or {})
         self.bias_suffix = params.get("bias_suffix", ".bias")
+        self.biases = bool(params.get("biases", True))
         self.group = INTERLEAVE if self.inter % INTERLEAVE == 0 else self.inter
         self.gate_up = self.down = self.gate_up_bias = self.output_bias = None
 
     def weight_shapes(self):
         n, b = self.names, self.bias_suffix
-        return {n["gate"]: (self.inter, self.hidden), n["up"]: (self.inter, self.hidden), n["down"]: (self.hidden, self.inter),
-                n["gate"] + b: (self.inter,), n["up"] + b: (self.inter,), n["down"] + b: (self.hidden,)}
+        shapes = {n["gate"]: (self.inter, self.hidden), n["up"]: (self.inter, self.hidden), n["down"]: (self.hidden, self.inter)}
+        if self.biases:
+            shapes.update({n["gate"] + b: (self.inter,), n["up"] + b: (self.inter,), n["down"] + b: (self.hidden,)})
+        return shapes
 
     def keeps_dtype(self, name):
-        return name.endswith(self.bias_suffix) and name[:-len(self.bias_suffix)] in self.names.values()
+        return self.biases and name.endswith(self.bias_suffix) and name[:-len(self.bias_suffix)] in self.names.values()
 
     def norm_like(self, name):
         return False
@@ -176,9 +181,13 @@ class LimitedGatedMLP(FeedForward):
         k = self.inter // self.group
         stack = lambda g, u, *rest: torch.stack([g.view(k, self.group, *rest), u.view(k, self.group, *rest)], 1)
         self.gate_up = stack(tensors[n["gate"]], tensors[n["up"]], self.hidden).reshape(2 * self.inter, self.hidden).contiguous()
-        self.gate_up_bias = stack(tensors[n["gate"] + b].float(), tensors[n["up"] + b].float()).reshape(2 * self.inter).contiguous()
         self.down = tensors[n["down"]].contiguous()
-        self.output_bias = tensors[n["down"] + b].float().contiguous()
+        if self.biases:
+            self.gate_up_bias = stack(tensors[n["gate"] + b].float(), tensors[n["up"] + b].float()).reshape(2 * self.inter).contiguous()
+            self.output_bias = tensors[n["down"] + b].float().contiguous()
+        else:                                           # the kernels take a bias vector: zeros
+            self.gate_up_bias = torch.zeros(2 * self.inter, dtype=torch.float32, device=self.down.device)
+            self.output_bias = None
 
     def streams_first(self, rows):
         return self.gate_up if self.dtype == torch.bfloat16 and rows <= ops.SKINNY_MAX_ROWS else None
@@ -203,7 +212,7 @@ class LimitedGatedMLP(FeedForward):
             ops.glu_limited(gu, self.gate_up_bias, act, self.group, self.limit, self.alpha)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(act, self.down, out, ctx.status)
-        if add_bias:
+        if add_bias and self.output_bias is not None:
             ops.add_bias(out, self.output_bias)
         return out
 

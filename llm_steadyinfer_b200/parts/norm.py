@@ -3,6 +3,8 @@ written back to the fp32 residual stream. Formula of the reference's
 ``row_rmsnorm_f32_dim`` (src/source/op/kernels/cuda/rmsnorm_kernel.cu:8-60), whose eps is a
 constant in the kernel; here it is a parameter of the part. With ``scalar`` the checkpoint holds one number
 for all coordinates (a tensor without dimensions), which is spread over the width when the weights are loaded.
+With ``offset`` c the checkpoint's vector is stored around zero and the norm multiplies by ``c + weight`` (summed in fp32
+when the weights are loaded, and kept in fp32).
 """
 from __future__ import annotations
 
@@ -24,6 +26,7 @@ class RMSNorm(Norm):
         self.eps = float(params["eps"])
         self.name = params.get("weight_name", "weight")      # "" where the checkpoint names the vector by the prefix alone
         self.scalar = bool(params.get("scalar", False))     # one number for all coordinates
+        self.offset = float(params.get("offset", 0.0))      # added to the stored vector
         self.weight: Optional[torch.Tensor] = None
 
     def weight_shapes(self):
@@ -34,7 +37,12 @@ class RMSNorm(Norm):
 
     def load_weights(self, tensors):
         w = tensors[self.name]
+        if self.offset:
+            w = w.float() + self.offset
         self.weight = (w.reshape(1).expand(self.size) if self.scalar else w).contiguous()
+
+    def norm_like(self, name):
+        return not self.offset                       # a vector stored around zero is drawn around zero
 
     def kernel_files(self, page_size):
         return ("norm",)
