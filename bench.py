@@ -294,6 +294,28 @@ def _vibunex_config(size="base"):
             "layers": [one] * 8}
 
 
+# ---- the Fevosun design beside the closest existing models ---------------------------------------------------
+# Sizes as the Vibunex section's (--design-size): attention of `heads` heads of 128 over `kv` key heads that are their own values,
+# window 4,096, a temperature step every 1,024 positions; latent attention of `heads` heads (128 plain + 64 rotated entries,
+# values of 128) over a latent of 512 (and a query latent of 768 in its second form); the first layer's feed-forward dense,
+# the others routed: 2 of (experts + 2 identity experts) of `eff` and a shared one of `sff`.
+def _fevosun_config(size="base"):
+    width, ff, heads, kv, _, experts, eff, sff = _VIBUNEX_SIZES[size]
+    window = {"size": 4096}
+    att = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": window,
+           "q_temp": {"coef": 0.5, "every": 1024}}
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5, "mask": window,
+           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    lat2 = dict(lat, q_rank=768, rot={"base": 10000.0, "dims": 64})
+    routed = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": experts, "identity": 2, "top": 2},
+              "shared": {"ff": sff, "limit": 7.0}}
+    one = [{"type": "attention", "mixer": att, "mlp": routed}, {"type": "latent_attention", "mixer": lat, "mlp": routed},
+           {"type": "attention", "mixer": att, "mlp": routed}, {"type": "latent_attention_2", "mixer": lat2, "mlp": routed}]
+    first = dict(one[0], mlp={"kind": "dense", "ff": ff})
+    return {"architecture": "Fevosun", "vocab": MIVORAX_VOCAB, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0},
+            "layers": [first] + one[1:] + one}, {"attention": att, "latent": lat, "latent_2": lat2, "feed_forward": routed}
+
+
 def mivorax_section(args, section="mivorax") -> int:
     """Prefill of 2,048 tokens and decode (batch 8, context 4,096) of an 8-layer Mivorax model (2 latent attention,
     4 attention with distance bias, 2 state-space layers; width 2,048) and of a Llama model of the same width, depth,
@@ -314,7 +336,16 @@ def mivorax_section(args, section="mivorax") -> int:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")        # larger than L2: written between timed steps
     results = {}
     width, ff = MIVORAX_WIDTH, MIVORAX_FF
-    if section == "vibunex":
+    if section == "fevosun":
+        # 8 layers (4 attention whose values are its keys, 2 + 2 latent attention; one dense and 7 routed feed-forwards with 5,632
+        # active entries a token, as the other models' feed-forwards) beside the Mivorax model (its closest in the mixers), the
+        # Vibunex model (its closest in the feed-forward) and the Llama model of the same width, depth and vocabulary
+        # (--design-size narrow / wide: beside the Vibunex and Llama models of that size)
+        width, ff, heads, kv = _VIBUNEX_SIZES[args.design_size][:4]
+        fev, mixers = _fevosun_config(args.design_size)
+        designs = (("fevosun", fev),) + ((("mivorax", _mivorax_config()),) if args.design_size == "base" else ()) \
+            + (("vibunex", _vibunex_config(args.design_size)), ("llama", _llama_twin(width, ff, heads, kv)))
+    elif section == "vibunex":
         # 8 layers, each a pair of mixers (attention of 16 heads of 128 over 4 key/value heads, weights mixed over the heads;
         # time mixing of 32 heads of 64 x 64) beside a routed feed-forward (2 of 16 experts of 1,408 and a shared one of 2,816:
         # 5,632 active a token, as the other models' feed-forwards), beside the Nufasun and Llama models of the same width
@@ -449,15 +480,16 @@ def main() -> int:
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed region of --section with cudaProfilerStart/Stop "
                          "(for ncu --profile-from-start off)")
-    ap.add_argument("--section", default="all", choices=["all", "decode", "prefill", "mivorax", "nufasun", "vibunex"],
+    ap.add_argument("--section", default="all", choices=["all", "decode", "prefill", "mivorax", "nufasun", "vibunex", "fevosun"],
                     help="run only the device-timed decode steps or only the prefill (for profiling); 'mivorax': prefill "
                          "and decode of a Mivorax model at layer sizes of a real model beside a Llama model of equal "
                          "width, with time per kind of kernel (its own JSON line; the default workload is not run); "
                          "'nufasun': the same for a Nufasun model beside the Mivorax and Llama models; 'vibunex': the same for a "
-                         "Vibunex model beside the Nufasun and Llama models")
+                         "Vibunex model beside the Nufasun and Llama models; 'fevosun': the same for a Fevosun model beside the "
+                         "Mivorax, Vibunex and Llama models")
     ap.add_argument("--design-size", default="base", choices=["narrow", "base", "wide"],
-                    help="--section vibunex: width 1,024 / 2,048 / 4,096 with heads, experts and feed-forward to match")
-    ap.add_argument("--only-design", default=None, help="--section mivorax / nufasun / vibunex: run this model alone (for profiling)")
+                    help="--section vibunex / fevosun: width 1,024 / 2,048 / 4,096 with heads, experts and feed-forward to match")
+    ap.add_argument("--only-design", default=None, help="--section mivorax / nufasun / vibunex / fevosun: run this model alone (for profiling)")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -466,7 +498,7 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     K, W = args.steps, max(3, args.warmup)
-    if args.section in ("mivorax", "nufasun", "vibunex"):
+    if args.section in ("mivorax", "nufasun", "vibunex", "fevosun"):
         return mivorax_section(args, args.section)
 
     import torch

@@ -81,36 +81,3 @@ SI_EXPORT int si_add_bias(void* x, long long stride, int dtype, const float* bia
     si_launch(add_bias_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)x, stride, bias, rows, width);
   return si_last_error();
 }
-
-// out[t, f] = a[t, f] * sigmoid(g[t, f]) (fp32 arithmetic): a gate on a mixer's heads, entry by entry. `a` is fp32 or
-// the compute dtype; `g` and `out` (which may be `a` itself) are in the compute dtype; all three are rows with a stride.
-template <typename TA, typename T>
-__global__ void sigmoid_gate_kernel(const TA* __restrict__ a, long long a_stride, const T* __restrict__ g, long long g_stride,
-                                    T* __restrict__ out, long long out_stride, int rows, int width) {
-  pdl_prologue();
-  const long long n = (long long)rows * width;
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
-    const long long t = idx / width, f = idx % width;
-    const float z = to_f32<T>(g[t * g_stride + f]);
-    out[t * out_stride + f] = from_f32<T>(to_f32<TA>(a[t * a_stride + f]) / (1.f + expf(-z)));
-  }
-}
-
-SI_EXPORT int si_sigmoid_gate(const void* a, int a_f32, long long a_stride, const void* g, long long g_stride, void* out,
-                              long long out_stride, int dtype, int rows, int width, cudaStream_t stream) {
-  if (rows <= 0 || width <= 0) return 0;
-  const long long n = (long long)rows * width;
-  const int threads = 256;
-  const long long want = (n + threads - 1) / threads;
-  const dim3 grid((unsigned)(want < 8LL * si_sm_count() ? want : 8LL * si_sm_count())), block(threads);
-  if (dtype == SI_BF16 && a_f32)
-    si_launch(sigmoid_gate_kernel<float, __nv_bfloat16>, grid, block, 0, stream, (const float*)a, a_stride, (const __nv_bfloat16*)g,
-              g_stride, (__nv_bfloat16*)out, out_stride, rows, width);
-  else if (dtype == SI_BF16)
-    si_launch(sigmoid_gate_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)a, a_stride,
-              (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, rows, width);
-  else
-    si_launch(sigmoid_gate_kernel<float, float>, grid, block, 0, stream, (const float*)a, a_stride, (const float*)g, g_stride,
-              (float*)out, out_stride, rows, width);
-  return si_last_error();
-}

@@ -1,7 +1,7 @@
 // bf16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, fp32 accumulation, fp32 online
 // softmax) in the general form of attention_general.cu: key size dk and value size dv of any multiple of 8,
 // values of their own or the first dv entries of the keys (a latent that is key and value), a bias by distance
-// added to the scaled score, a penalty slope[h] * (i - j) taken off it, a query temperature by position (row i's scale
+// added to the scaled score, an output gate (the result times sigmoid of a row of gate sums), a penalty slope[h] * (i - j) taken off it, a query temperature by position (row i's scale
 // times 1 + coef * ln(floor((i + 1) / every) + 1)), a sink per head in the denominator, a soft limit on the scaled score
 // (s <- cap * tanh(s / cap)), key heads that share a value head (v_share neighbouring key heads read one of the
 // KV / v_share value heads), results in fp32 where the caller goes on computing with them. One kernel serves prompt
@@ -33,6 +33,7 @@ struct FlexParams {
   const float* sink;                             // fp32 [H] or nullptr
   const float* slopes;                           // fp32 [H] or nullptr: slope[h] * distance leaves the scaled score
   float qt_coef; int qt_every;                   // query temperature (every 0: none)
+  const bf16* gate; long long gate_stride;       // not null: the result (row, head, d) times sigmoid(gate[row, head * dv + d])
   int num_pages, page_size, num_seqs, H, KV, G, Gb, hparts, dk, dv, dk_pitch;
   int bias_in_smem;         // the distances a key tile can meet are staged in shared memory, tile by tile
   int warps_are_slices;     // items of at most 16 rows whose values are key columns: every warp takes rows 0..15 and a
@@ -359,12 +360,18 @@ attn_flex_kernel(const FlexParams p) {
     }
     const float inv = l > 0.f ? f / l : 0.f;
     const size_t at = (size_t)(item.row0 + tok) * p.out_stride + (size_t)(head0 + hh) * p.dv;
+    const bf16* grow = p.gate ? p.gate + (size_t)(item.row0 + tok) * p.gate_stride + (size_t)(head0 + hh) * p.dv : nullptr;
 #pragma unroll
     for (int dt = 0; dt < DT; ++dt) {
       const int d = v0 + dt * 8 + (lane & 3) * 2;
       if (d >= p.dv) continue;
-      if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + at + d) = make_float2(o[dt][half * 2] * inv, o[dt][half * 2 + 1] * inv);
-      else *reinterpret_cast<__nv_bfloat162*>(p.out + at + d) = __floats2bfloat162_rn(o[dt][half * 2] * inv, o[dt][half * 2 + 1] * inv);
+      float r0 = o[dt][half * 2] * inv, r1 = o[dt][half * 2 + 1] * inv;
+      if (grow) {
+        const float2 gz = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(grow + d));
+        r0 /= 1.f + __expf(-gz.x); r1 /= 1.f + __expf(-gz.y);
+      }
+      if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + at + d) = make_float2(r0, r1);
+      else *reinterpret_cast<__nv_bfloat162*>(p.out + at + d) = __floats2bfloat162_rn(r0, r1);
     }
   }
 }
@@ -407,8 +414,10 @@ __global__ void attn_flex_merge_kernel(const FlexParams p) {
 #pragma unroll
       for (int u = 0; u < 8; ++u) acc = fmaf(v[u], s0 + u < p.nsplit ? w[s0 + u] : 0.f, acc);
     }
-    if (p.out_f32) p.out_f32[at + d] = acc * s_inv;
-    else p.out[at + d] = __float2bfloat16_rn(acc * s_inv);
+    float res = acc * s_inv;
+    if (p.gate) res /= 1.f + __expf(-__bfloat162float(p.gate[(size_t)(item.row0 + tok) * p.gate_stride + (size_t)head * p.dv + d]));
+    if (p.out_f32) p.out_f32[at + d] = res;
+    else p.out[at + d] = __float2bfloat16_rn(res);
   }
 }
 
@@ -450,12 +459,15 @@ SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cach
                            long long out_stride, int num_pages, int page_size, int num_seqs, int H, int KV, int dk,
                            int dv, float scale, int window, const float* dist_bias, int nd, const float* sink,
                            int nsplit, float* scratch, int max_rows, float softcap, int v_share, int out_is_f32,
-                           const float* slopes, float qt_coef, int qt_every, int* status, cudaStream_t stream) {
+                           const float* slopes, float qt_coef, int qt_every, const void* gate, long long gate_stride,
+                           int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
   if (!si_attn_flex_ok(H, KV, dk, dv, v_cache != nullptr) || nsplit < 1 || nsplit > 64 || (nsplit > 1 && !scratch)) return -2;
   if (v_share < 1 || KV % v_share || (v_share > 1 && !v_cache) || softcap < 0.f || qt_every < 0) return -2;
   FlexParams p;
   p.slopes = slopes; p.qt_coef = qt_coef; p.qt_every = qt_every;
+  p.gate = (const bf16*)gate; p.gate_stride = gate_stride;
+  if (gate && (gate_stride % 2 || ((uintptr_t)gate & 3))) return -2;      // the gate is read two entries at a time
   p.q = (const bf16*)q; p.q_stride = q_stride;
   p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = block_table; p.table_width = table_width;

@@ -7,6 +7,7 @@
 //   * a sink per head: exp(sink[h]) joins the softmax denominator once, with no key and no value,
 //   * a penalty in proportion to the distance: slope[h] * (i - j) taken off the scaled score (fp32 [H]),
 //   * a query temperature by position: the scale of row i is multiplied by 1 + coef * ln(floor((i + 1) / every) + 1),
+//   * an output gate: the result's entry (row, head, d) is multiplied by sigmoid(gate[row, head * dv + d]),
 //   * a soft limit on the scaled score: s <- softcap * tanh(s / softcap) (before the bias),
 //   * key heads that share a value head: `v_share` neighbouring key heads read one value head (the cache then holds
 //     KV / v_share value heads), as the maps of a differential attention do,
@@ -35,7 +36,8 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
                          int page_size, int num_seqs, int H, int KV, int dk, int dv, float scale,
                          int window, const float* __restrict__ dist_bias, int nd,
                          const float* __restrict__ sink, float softcap, int v_share,
-                         const float* __restrict__ slopes, float qt_coef, int qt_every, int* status) {
+                         const float* __restrict__ slopes, float qt_coef, int qt_every,
+                         const T* __restrict__ gate, long long gate_row_stride, int* status) {
   extern __shared__ float smem[];   // [GEN_WARPS][dv] accumulators, then m[GEN_WARPS], l[GEN_WARPS]
   const int t = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -119,7 +121,9 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < GEN_WARPS; ++w) v += sacc[w * dv + d] * wgt[w];
-    o[d] = from_f32<TO>(L > 0.f ? v / L : 0.f);
+    v = L > 0.f ? v / L : 0.f;
+    if (gate) v /= 1.f + expf(-to_f32<T>(gate[(size_t)t * gate_row_stride + (size_t)h * dv + d]));
+    o[d] = from_f32<TO>(v);
   }
 }
 
@@ -129,8 +133,8 @@ SI_EXPORT int si_attention_general(const void* q, int dtype, long long q_row_str
                                    long long out_row_stride, int num_pages, int page_size, int num_tokens,
                                    int num_seqs, int H, int KV, int dk, int dv, float scale, int window,
                                    const float* dist_bias, int nd, const float* sink, float softcap, int v_share,
-                                   int out_f32, const float* slopes, float qt_coef, int qt_every, int* status,
-                                   cudaStream_t stream) {
+                                   int out_f32, const float* slopes, float qt_coef, int qt_every, const void* gate,
+                                   long long gate_row_stride, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (dk > 32 * GEN_WIDE_PER_LANE || dv > 32 * GEN_WIDE_PER_LANE || dk <= 0 || dv <= 0 || KV <= 0 || H % KV) return -2;
   if (!v_cache && dv > dk) return -2;
@@ -143,7 +147,7 @@ SI_EXPORT int si_attention_general(const void* q, int dtype, long long q_row_str
   attention_general_kernel<T, TO, PL><<<grid, GEN_WARPS * 32, smem, stream>>>(                                         \
       (const T*)q, q_row_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_width, row_seq, positions,   \
       (TO*)out, out_row_stride, num_pages, page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink,     \
-      softcap, v_share, slopes, qt_coef, qt_every, status)
+      softcap, v_share, slopes, qt_coef, qt_every, (const T*)gate, gate_row_stride, status)
   if (dk > 32 * GEN_MAX_PER_LANE || dv > 32 * GEN_MAX_PER_LANE) {        // sizes above 640: the kernel with more entries a lane
     if (dtype == SI_BF16 && out_f32) GEN_LAUNCH(__nv_bfloat16, float, GEN_WIDE_PER_LANE);
     else if (dtype == SI_BF16) GEN_LAUNCH(__nv_bfloat16, __nv_bfloat16, GEN_WIDE_PER_LANE);
@@ -317,8 +321,8 @@ SI_EXPORT int si_latent_prepare(const void* kv, int dtype, long long kv_stride, 
 }
 
 // ---- the latent form expanded for long prompt portions -------------------------------------------------------
-// For the sequences listed in `seqs` ([E, 3] rows of (sequence of the step, first dense row, keys)), the cached
-// [latent | shared key part] rows of positions 0 .. keys-1 are copied out of the pages into consecutive dense rows,
+// For the sequences listed in `seqs` ([E, 4] rows of (sequence of the step, first dense row, keys, first position)), the cached
+// [latent | shared key part] rows of positions first .. first + keys - 1 are copied out of the pages into consecutive dense rows,
 // where a matrix product can expand them into keys and values per head. One block per 8 keys of a sequence.
 template <typename T>
 __global__ void latent_gather_kernel(const T* __restrict__ k_cache, const int* __restrict__ block_table, int table_width,
@@ -326,11 +330,11 @@ __global__ void latent_gather_kernel(const T* __restrict__ k_cache, const int* _
                                      int num_seqs, int width, int* status) {
   pdl_prologue();
   const int e = blockIdx.y;
-  const int seq = seqs[3 * e], row0 = seqs[3 * e + 1], keys = seqs[3 * e + 2];
+  const int seq = seqs[4 * e], row0 = seqs[4 * e + 1], keys = seqs[4 * e + 2], first = seqs[4 * e + 3];
   for (int j = blockIdx.x * 8; j < min(keys, blockIdx.x * 8 + 8); ++j) {
-    const long long page = page_of(block_table, table_width, num_pages, page_size, num_seqs, seq, j, status);
+    const long long page = page_of(block_table, table_width, num_pages, page_size, num_seqs, seq, first + j, status);
     if (page < 0) continue;
-    const T* src = k_cache + ((size_t)page * page_size + j % page_size) * width;
+    const T* src = k_cache + ((size_t)page * page_size + (first + j) % page_size) * width;
     T* dst = dense + (size_t)(row0 + j) * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
   }

@@ -67,7 +67,7 @@ __device__ __forceinline__ void add_row32(float* dst, const float (&v)[32], int 
 }
 
 // What the epilogue does with a tile: store it, store silu(gate) * up of it, or add it into an fp32 tensor.
-enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2, EPI_RELU2 = 3, EPI_GLU_LIMITED = 4 };
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2, EPI_RELU2 = 3, EPI_GLU_LIMITED = 4, EPI_GLU_PAIRS = 5 };
 
 // What EPI_GLU_LIMITED needs: the biases of the stacked gate/up columns (fp32, in the columns' order; may be null), the
 // limit and the sigmoid's factor.
@@ -80,6 +80,31 @@ __device__ __forceinline__ void relu2_row32(float (&v)[32]) {
   for (int i = 0; i < 32; ++i) {
     const float r = fmaxf(__bfloat162float(__float2bfloat16_rn(v[i])), 0.f);
     v[i] = r * r;
+  }
+}
+
+// The gated activation with limits where gate and up columns come in turn (column 2i an entry's gate sum, column 2i + 1
+// its up sum; no biases): 16 outputs from 32 accumulator columns, gate and up rounded to bf16 first.
+__device__ __forceinline__ void store_glu_pairs16(bf16* dst, const float (&v)[32], float limit, float alpha, int valid, bool vec) {
+  float o[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float gv = fminf(__bfloat162float(__float2bfloat16_rn(v[2 * i])), limit);
+    const float uv = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(v[2 * i + 1])), -limit), limit);
+    o[i] = gv / (1.f + __expf(-alpha * gv)) * (uv + 1.f);
+  }
+  if (vec && valid == 16) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint4 raw;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[8 * i + 2 * j], o[8 * i + 2 * j + 1]);
+      reinterpret_cast<uint4*>(dst)[i] = raw;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) if (i < valid) dst[i] = __float2bfloat16_rn(o[i]);
   }
 }
 
@@ -509,7 +534,8 @@ static int gemm_tc05_common(const void* x, long long ldx, const void* wmap, CUte
 template <int STAGES, typename TO, int EPI>
 __global__ void __launch_bounds__(192)
 gemm_tc05_grouped_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
-                         TO* __restrict__ out, long long ldo, const int* __restrict__ offsets, int E, int N, int K, int* status) {
+                         TO* __restrict__ out, long long ldo, const int* __restrict__ offsets, int E, int N, int K, int* status,
+                         const EpiArgs epi) {
   constexpr int BM = 128, BN = 256, BK = 64;
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   extern __shared__ unsigned char smem_dyn[];
@@ -652,8 +678,12 @@ gemm_tc05_grouped_kernel(const __grid_constant__ CUtensorMap amap, const __grid_
         for (int c = 0; c < 4; ++c) {
           const int n = n0 + h * 128 + c * 32;
           if (r < rows && n < N) {
-            if (EPI == EPI_RELU2) relu2_row32(v[c]);
-            store_row32<TO>(out + (size_t)(first + r) * ldo + n, v[c], min(32, N - n), vec);
+            if (EPI == EPI_GLU_PAIRS) {              // out has N / 2 columns: an entry for every gate/up pair
+              store_glu_pairs16((bf16*)out + (size_t)(first + r) * ldo + n / 2, v[c], epi.limit, epi.alpha, min(16, (N - n) / 2), vec);
+            } else {
+              if (EPI == EPI_RELU2) relu2_row32(v[c]);
+              store_row32<TO>(out + (size_t)(first + r) * ldo + n, v[c], min(32, N - n), vec);
+            }
           }
         }
       }
@@ -666,7 +696,7 @@ gemm_tc05_grouped_kernel(const __grid_constant__ CUtensorMap amap, const __grid_
 
 template <typename TO, int EPI>
 static int launch_grouped(const CUtensorMap& am, const CUtensorMap& bm, void* out, long long ldo, const int* offsets, int P,
-                          int E, int N, int K, int* status, cudaStream_t stream) {
+                          int E, int N, int K, int* status, cudaStream_t stream, EpiArgs epi = EpiArgs{nullptr, 0.f, 0.f}) {
   constexpr int STAGES = 4;
   const size_t smem = (size_t)STAGES * (128 * 64 * 2 + 256 * 64 * 2) + 1024;
   auto k = gemm_tc05_grouped_kernel<STAGES, TO, EPI>;
@@ -674,7 +704,7 @@ static int launch_grouped(const CUtensorMap& am, const CUtensorMap& bm, void* ou
   if (e != cudaSuccess) return (int)e;
   const long long most = ((long long)(P + 127) / 128 + E) * ((N + 255) / 256);      // no more tiles than this, whatever the offsets
   const int blocks = most < si_sm_count() ? (int)most : si_sm_count();
-  si_launch(k, dim3(blocks), dim3(192), smem, stream, am, bm, (TO*)out, ldo, offsets, E, N, K, status);
+  si_launch(k, dim3(blocks), dim3(192), smem, stream, am, bm, (TO*)out, ldo, offsets, E, N, K, status, epi);
   return si_last_error();
 }
 
@@ -685,15 +715,19 @@ SI_EXPORT int si_gemm_tc05_grouped_ok(int P, int E) {
 
 // out[p, :] = act(x[p, :] W[e]^T) for the rows p of group e, offsets[e] <= p < offsets[e + 1] (int32 [E + 1] on the device,
 // offsets[E] <= P). x: [P, K] bf16 rows `ldx` apart; `wmap`: W [E, N, K] described as [E * N, K] with boxes of 256 rows;
-// out [P, N] bf16 or fp32; act 0: none, 1: the square of relu (of the sum rounded to bf16; bf16 out only).
+// out [P, N] bf16 or fp32; act 0: none, 1: the square of relu (of the sum rounded to bf16; bf16 out only), 2: the gated
+// activation with limits over gate/up columns in turn (out [P, N / 2] bf16; `limit`, `alpha`).
 SI_EXPORT int si_gemm_tc05_grouped(const void* x, long long ldx, const void* wmap, void* out, long long ldo, int out_dtype,
-                                   const int* offsets, int P, int E, int N, int K, int act, int* status, cudaStream_t stream) {
+                                   const int* offsets, int P, int E, int N, int K, int act, float limit, float alpha,
+                                   int* status, cudaStream_t stream) {
   if (P <= 0 || N <= 0) return 0;
-  if (!si_gemm_tc05_grouped_ok(P, E) || act < 0 || act > 1 || (act == 1 && out_dtype != SI_BF16)) return -2;
+  if (!si_gemm_tc05_grouped_ok(P, E) || act < 0 || act > 2 || (act >= 1 && out_dtype != SI_BF16)) return -2;
+  if (act == 2 && (N % 2 || !(limit > 0.f))) return -2;
   CUtensorMap am;
   const int rc = gemm_tc05_common(x, ldx, wmap, &am, P, K);
   if (rc) return rc;
   const CUtensorMap& bm = *(const CUtensorMap*)wmap;
+  if (act == 2) return launch_grouped<bf16, EPI_GLU_PAIRS>(am, bm, out, ldo, offsets, P, E, N, K, status, stream, EpiArgs{nullptr, limit, alpha});
   if (act == 1) return launch_grouped<bf16, EPI_RELU2>(am, bm, out, ldo, offsets, P, E, N, K, status, stream);
   if (out_dtype == SI_BF16) return launch_grouped<bf16, EPI_STORE>(am, bm, out, ldo, offsets, P, E, N, K, status, stream);
   return launch_grouped<float, EPI_STORE>(am, bm, out, ldo, offsets, P, E, N, K, status, stream);

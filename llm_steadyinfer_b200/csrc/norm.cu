@@ -47,7 +47,7 @@ template <> struct Vec8<__nv_bfloat16> {
 // CHUNKS: 8-element chunks per thread (hidden <= CHUNKS * 8 * blockDim.x)
 template <typename TX, typename TW, int CHUNKS>
 __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(float* __restrict__ resid, const TX* __restrict__ delta,
-                                       const int* __restrict__ rows, const TW* __restrict__ weight,
+                                       const TX* __restrict__ delta2, const int* __restrict__ rows, const TW* __restrict__ weight,
                                        TX* __restrict__ out, int hidden, float eps, int num_rows,
                                        const void* ahead, long long ahead_bytes, int trigger) {
   __shared__ float scratch[33];
@@ -61,15 +61,17 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(float* __restrict_
   const int src = rows ? rows[r] : r;
   float* h = resid + (size_t)src * hidden;
   const TX* dl = delta ? delta + (size_t)src * hidden : nullptr;
+  const TX* dl2 = (delta && delta2) ? delta2 + (size_t)src * hidden : nullptr;     // a second result of the same block
   const int nchunks = hidden >> 3;
   Vec8<float> x[CHUNKS];
-  Vec8<TX> dv[CHUNKS];
+  Vec8<TX> dv[CHUNKS], dv2[CHUNKS];
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
     const int ch = threadIdx.x + c * blockDim.x;
     if (ch < nchunks) {
       x[c].load(h + ch * 8);
       if (dl) dv[c].load(dl + ch * 8);
+      if (dl2) dv2[c].load(dl2 + ch * 8);
     }
   }
   float ss = 0.f;
@@ -80,6 +82,10 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(float* __restrict_
       if (dl) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[c].v[i] += dv[c].v[i];
+        if (dl2) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[c].v[i] += dv2[c].v[i];
+        }
         if (!rows) x[c].store(h + ch * 8);
       }
 #pragma unroll
@@ -104,7 +110,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(float* __restrict_
 }
 
 template <typename TX, typename TW>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TX* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TX* __restrict__ delta, const TX* __restrict__ delta2,
                                    const int* __restrict__ rows, const TW* __restrict__ weight,
                                    TX* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[33];
@@ -113,10 +119,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TX* __restri
   const int src = rows ? rows[r] : r;
   float* h = resid + (size_t)src * hidden;
   const TX* dl = delta ? delta + (size_t)src * hidden : nullptr;
+  const TX* dl2 = (delta && delta2) ? delta2 + (size_t)src * hidden : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = h[i];
     if (dl) v += to_f32<TX>(dl[i]);
+    if (dl2) v += to_f32<TX>(dl2[i]);
     row_cache[i] = v;
     if (dl && !rows) h[i] = v;
     ss += v * v;
@@ -129,12 +137,13 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TX* __restri
 }
 
 template <typename TX, typename TW>
-static int launch2(float* resid, const void* delta, const int* rows, const void* weight, void* out,
+static int launch2(float* resid, const void* delta, const void* delta2, const int* rows, const void* weight, void* out,
                    int num_rows, int hidden, float eps, const void* ahead, long long ahead_bytes, cudaStream_t stream) {
   const TX* d = (const TX*)delta;
+  const TX* d2 = (const TX*)delta2;
   const TW* w = (const TW*)weight;
   TX* o = (TX*)out;
-  const bool aligned = ((uintptr_t)resid % 16 == 0) && ((uintptr_t)delta % 16 == 0) &&
+  const bool aligned = ((uintptr_t)resid % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)delta2 % 16 == 0) &&
                        ((uintptr_t)weight % 16 == 0) && ((uintptr_t)out % 16 == 0);
   if (hidden % 8 == 0 && aligned && hidden <= 4 * 8 * 512) {
     const int nchunks = hidden / 8;
@@ -148,9 +157,9 @@ static int launch2(float* resid, const void* delta, const int* rows, const void*
     const int sms = si_sm_count();
     const int extra = ahead ? max(0, sms - num_rows) + sms : 0;
     const dim3 grid(num_rows + extra);
-    if (per <= 1) si_launch(add_rmsnorm_vec_kernel<TX, TW, 1>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
-    else if (per <= 2) si_launch(add_rmsnorm_vec_kernel<TX, TW, 2>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
-    else si_launch(add_rmsnorm_vec_kernel<TX, TW, 4>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
+    if (per <= 1) si_launch(add_rmsnorm_vec_kernel<TX, TW, 1>, grid, dim3(threads), 0, stream, resid, d, d2, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
+    else if (per <= 2) si_launch(add_rmsnorm_vec_kernel<TX, TW, 2>, grid, dim3(threads), 0, stream, resid, d, d2, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
+    else si_launch(add_rmsnorm_vec_kernel<TX, TW, 4>, grid, dim3(threads), 0, stream, resid, d, d2, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
     return si_last_error();
   }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -158,25 +167,26 @@ static int launch2(float* resid, const void* delta, const int* rows, const void*
   if (smem > 200 * 1024) return -2;           // hidden too large for the row cache
   auto k = add_rmsnorm_kernel<TX, TW>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  k<<<num_rows, threads, smem, stream>>>(resid, d, rows, w, o, hidden, eps);
+  k<<<num_rows, threads, smem, stream>>>(resid, d, d2, rows, w, o, hidden, eps);
   return si_last_error();
 }
 
-// x_dtype: dtype of delta and out. `ahead` (may be null): `ahead_bytes` bytes that the kernel after this
+// x_dtype: dtype of delta, delta2 and out; `delta2` (may be null, and counts only beside `delta`): a second result that
+// joins the stream in the same sum, h = (resid + delta) + delta2. `ahead` (may be null): `ahead_bytes` bytes that the kernel after this
 // one streams, fetched into L2 meanwhile (a hint: the vectorised kernel takes it, the other one ignores it).
 // Returns 0, a CUDA error code, or -2 (size refused).
-SI_EXPORT int si_add_rmsnorm(float* resid, const void* delta, const int* rows, const void* weight,
+SI_EXPORT int si_add_rmsnorm(float* resid, const void* delta, const void* delta2, const int* rows, const void* weight,
                              int weight_dtype, void* out, int x_dtype, int num_rows, int hidden,
                              float eps, const void* ahead, long long ahead_bytes, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (x_dtype == SI_BF16) {
     if (weight_dtype == SI_BF16)
-      return launch2<__nv_bfloat16, __nv_bfloat16>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
-    return launch2<__nv_bfloat16, float>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
+      return launch2<__nv_bfloat16, __nv_bfloat16>(resid, delta, delta2, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
+    return launch2<__nv_bfloat16, float>(resid, delta, delta2, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
   }
   if (weight_dtype == SI_BF16)
-    return launch2<float, __nv_bfloat16>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
-  return launch2<float, float>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
+    return launch2<float, __nv_bfloat16>(resid, delta, delta2, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
+  return launch2<float, float>(resid, delta, delta2, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
 }
 
 // ---- a norm that is not on the residual stream ------------------------------------------------------------------

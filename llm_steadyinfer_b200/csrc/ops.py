@@ -148,16 +148,19 @@ def embedding_gather(tokens, table, out, status=None, scale: float = 1.0) -> Non
 AHEAD_BYTES = int(os.environ.get("SI_AHEAD_MB", "4")) << 20
 
 
-def add_rmsnorm(resid, delta, weight, eps: float, out, rows=None, ahead=None) -> None:
-    """resid (fp32, in place) += delta; out = weight * resid * rsqrt(mean(resid^2) + eps).
+def add_rmsnorm(resid, delta, weight, eps: float, out, rows=None, ahead=None, delta2=None) -> None:
+    """resid (fp32, in place) += delta (+ delta2); out = weight * resid * rsqrt(mean(resid^2) + eps).
 
     With ``rows`` (int32 [R]) output row r comes from stream row rows[r] and resid stays
     as it is. ``ahead``: a tensor that the kernel after this one streams from memory (weights of
     the next matrix product); further blocks of this launch start fetching it into L2.
     """
-    _cuda(resid, delta, weight, out, rows)
+    _cuda(resid, delta, weight, out, rows, delta2)
     _i32(rows, "rows")
     d = resid.shape[-1]
+    if delta2 is not None:
+        _need(delta is not None and delta2.dtype == out.dtype and delta2.is_contiguous() and delta2.shape == resid.shape,
+              "add_rmsnorm: delta2 goes beside delta and must match resid's shape and out's dtype")
     _need(resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous()
           and weight.is_contiguous(), "add_rmsnorm: tensors must be contiguous, resid fp32")
     _need(weight.numel() == d and out.shape[-1] == d, "add_rmsnorm: width mismatch")
@@ -167,12 +170,12 @@ def add_rmsnorm(resid, delta, weight, eps: float, out, rows=None, ahead=None) ->
     R = out.shape[0]
     _need(R == (rows.numel() if rows is not None else resid.shape[0]), "add_rmsnorm: row count mismatch")
     f = _fn("norm", "si_add_rmsnorm",
-            [_c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p, _c_ll, _c_p])
+            [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p, _c_ll, _c_p])
     ahead_bytes = 0
     if ahead is not None:
         _cuda(ahead)
         ahead_bytes = min(ahead.numel() * ahead.element_size(), AHEAD_BYTES) if ahead.is_contiguous() else 0
-    _check(f(_ptr(resid), _ptr(delta), _ptr(rows), _ptr(weight), _dt(weight), _ptr(out), _dt(out),
+    _check(f(_ptr(resid), _ptr(delta), _ptr(delta2), _ptr(rows), _ptr(weight), _dt(weight), _ptr(out), _dt(out),
              R, d, float(eps), _ptr(ahead) if ahead_bytes else None, ahead_bytes, _stream()), f"add_rmsnorm(hidden={d})")
 
 
@@ -949,15 +952,18 @@ def _q_temp(q_temp):
 
 def attention_general(q, k_cache, v_cache, block_table, row_seq, positions, out, page_size: int, num_seqs: int,
                       H: int, KV: int, dk: int, dv: int, scale: float, window: int = 0, dist_bias=None, sink=None,
-                      status=None, softcap: float = 0.0, v_share: int = 1, slopes=None, q_temp=None) -> None:
+                      status=None, softcap: float = 0.0, v_share: int = 1, slopes=None, q_temp=None, gate=None) -> None:
     """fp32-arithmetic attention over the paged cache with key size ``dk``, value size ``dv``, values from
     ``v_cache`` or (None) the first ``dv`` entries of the keys, a bias by distance ``dist_bias`` (fp32 [nd, H],
     row min(distance, nd - 1)) and a sink per head (fp32 [H]) in the softmax denominator. ``softcap`` > 0: the scaled
     score s becomes softcap * tanh(s / softcap). ``v_share`` > 1: that many neighbouring key heads read one value head
     (``v_cache`` holds KV / v_share heads). ``slopes`` (fp32 [H]): ``slopes[h] * (i - j)`` is taken off the scaled score of
     query i and key j. ``q_temp`` ``(coef, every)``: row i's scale is multiplied by 1 + coef * ln(floor((i + 1) / every) + 1).
+    ``gate`` ([T, H*dv] like ``q``, rows with a stride): the result is multiplied entry by entry with sigmoid(gate).
     ``out`` may be fp32 whatever the storage."""
-    _cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, dist_bias, sink, slopes, status)
+    _cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, dist_bias, sink, slopes, gate, status)
+    _need(gate is None or (gate.dtype == q.dtype and gate.shape == (q.shape[0], H * dv) and gate.stride(1) == 1),
+          "attention_general: gate must be [T, H*dv] in q's dtype")
     _f32v(slopes, "slopes", H)
     qt_coef, qt_every = _q_temp(q_temp)
     _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
@@ -981,12 +987,12 @@ def attention_general(q, k_cache, v_cache, block_table, row_seq, positions, out,
     f = _fn("attention_general", "si_attention_general",
             [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int,
              _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_f, _c_int, _c_int, _c_p, _c_f, _c_int,
-             _c_p, _c_p])
+             _c_p, _c_ll, _c_p, _c_p])
     _check(f(_ptr(q), _dt(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(row_seq), _ptr(positions), _ptr(out), out.stride(0), k_cache.shape[0], page_size, T, num_seqs,
              H, KV, dk, dv, float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), float(softcap or 0.0),
              int(v_share), 1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0, _ptr(slopes), qt_coef,
-             qt_every, _ptr(status), _stream()),
+             qt_every, _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(status), _stream()),
            f"attention_general(dk={dk}, dv={dv})")
 
 
@@ -1063,17 +1069,6 @@ def activation(x, out, kind: str) -> None:
 
 
 # ---- state-space mixer ---------------------------------------------------------------------------------
-
-def sigmoid_gate(a, gate, out) -> None:
-    """out = a * sigmoid(gate) entry by entry (fp32 arithmetic): ``a`` [T, W] in fp32 or out's dtype, ``gate`` and ``out`` [T, W]
-    in the compute dtype, all rows with a stride (views into a stacked projection); ``out`` may be ``a``."""
-    _cuda(a, gate, out)
-    _need(a.dim() == 2 and gate.shape == a.shape and out.shape == a.shape and a.stride(1) == 1 and gate.stride(1) == 1
-          and out.stride(1) == 1 and gate.dtype == out.dtype and a.dtype in (out.dtype, torch.float32), "sigmoid_gate: shapes or dtypes")
-    f = _fn("activation", "si_sigmoid_gate", [_c_p, _c_int, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p])
-    _check(f(_ptr(a), 1 if a.dtype == torch.float32 and out.dtype != torch.float32 else 0, a.stride(0), _ptr(gate), gate.stride(0),
-             _ptr(out), out.stride(0), _dt(out), a.shape[0], a.shape[1], _stream()), "sigmoid_gate")
-
 
 def causal_conv(u, weight, bias, state, conv_off: int, out, positions, row_seq, q_start, ctx_len, slots,
                 num_seqs: int, status=None) -> None:
@@ -1183,14 +1178,16 @@ def attn_flex_scratch_floats(num_items: int, H: int, KV: int, dv: int, nsplit: i
 
 def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int, dk: int,
               dv: int, scale: float, window: int = 0, dist_bias=None, sink=None, nsplit: int = 1, scratch=None,
-              status=None, max_rows: int = 0, softcap: float = 0.0, v_share: int = 1, slopes=None, q_temp=None) -> None:
+              status=None, max_rows: int = 0, softcap: float = 0.0, v_share: int = 1, slopes=None, q_temp=None, gate=None) -> None:
     """``attention_general`` on the tensor cores for bfloat16. ``items``: int32 [n, 4] rows (sequence, first row,
     tokens, first position) of at most ``attn_flex_tokens`` tokens. ``nsplit`` > 1 cuts every item's keys into that
     many shares (decode rows over long contexts); ``scratch`` then holds ``attn_flex_scratch_floats`` floats.
     ``max_rows``: the most rows (tokens x query heads of a key head served together) of any item when the caller knows it
     (0: unknown); at most 16 rows over keys that are their own values let a block's warps take a value slice each.
-    ``softcap``, ``v_share``, ``slopes``, ``q_temp`` as in ``attention_general``; ``out`` may be fp32."""
-    _cuda(q, k_cache, v_cache, block_table, items, out, dist_bias, sink, scratch, slopes, status)
+    ``softcap``, ``v_share``, ``slopes``, ``q_temp``, ``gate`` as in ``attention_general``; ``out`` may be fp32."""
+    _cuda(q, k_cache, v_cache, block_table, items, out, dist_bias, sink, scratch, slopes, gate, status)
+    _need(gate is None or (gate.dtype == torch.bfloat16 and gate.shape == (q.shape[0], H * dv) and gate.stride(1) == 1
+                           and gate.stride(0) % 2 == 0 and gate.data_ptr() % 4 == 0), "attn_flex: gate must be bf16 [T, H*dv], rows 4-byte aligned")
     _f32v(slopes, "slopes", H)
     qt_coef, qt_every = _q_temp(q_temp)
     _i32(block_table, "block_table"); _i32(items, "items")
@@ -1220,12 +1217,12 @@ def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_
     f = _fn("attention_flex", "si_attn_flex",
             [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int,
              _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_f, _c_int, _c_int, _c_p, _c_f, _c_int,
-             _c_p, _c_p])
+             _c_p, _c_ll, _c_p, _c_p])
     _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(items),
              items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs, H, KV, dk, dv,
              float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), int(nsplit), _ptr(scratch), int(max_rows),
              float(softcap or 0.0), int(v_share), 1 if out.dtype == torch.float32 else 0, _ptr(slopes), qt_coef, qt_every,
-             _ptr(status), _stream()), f"attn_flex(heads={H}, kv_heads={KV}, dk={dk}, dv={dv})", kernels=2 if nsplit > 1 else 1)
+             _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(status), _stream()), f"attn_flex(heads={H}, kv_heads={KV}, dk={dk}, dv={dv})", kernels=2 if nsplit > 1 else 1)
 
 
 # ---- one small matrix per head (decode rows) -----------------------------------------------------------------
@@ -1252,15 +1249,15 @@ def gemm_heads(a, w, out, a_head: int, o_head: int) -> None:
 
 
 def latent_gather(k_cache, block_table, seqs, max_keys: int, dense, page_size: int, num_seqs: int, status=None) -> None:
-    """Copies the cached rows of positions 0 .. keys-1 of the listed sequences out of the pages into consecutive rows
-    of ``dense`` [rows, width]. ``seqs``: int32 [E, 3] rows of (sequence of the step, first dense row, keys);
+    """Copies the cached rows of positions first .. first + keys - 1 of the listed sequences out of the pages into consecutive
+    rows of ``dense`` [rows, width]. ``seqs``: int32 [E, 4] rows of (sequence of the step, first dense row, keys, first position);
     ``max_keys``: the most keys of any of them. ``k_cache`` [pages, 1, page_size, width]."""
     _cuda(k_cache, block_table, seqs, dense, status)
     _i32(block_table, "block_table"); _i32(seqs, "seqs")
     width = k_cache.shape[3]
     _need(k_cache.is_contiguous() and k_cache.shape[1] == 1 and k_cache.shape[2] == page_size and dense.is_contiguous()
-          and dense.shape[1] == width and dense.dtype == k_cache.dtype and seqs.dim() == 2 and seqs.shape[1] == 3,
-          "latent_gather: cache [pages, 1, page_size, width], dense [rows, width], seqs [E, 3]")
+          and dense.shape[1] == width and dense.dtype == k_cache.dtype and seqs.dim() == 2 and seqs.shape[1] == 4,
+          "latent_gather: cache [pages, 1, page_size, width], dense [rows, width], seqs [E, 4]")
     f = _fn("attention_general", "si_latent_gather",
             [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
     _check(f(_ptr(k_cache), _dt(k_cache), _ptr(block_table), block_table.shape[1], _ptr(seqs), seqs.shape[0], int(max_keys),
@@ -1598,7 +1595,7 @@ def moe_plan(ids, E: int, scratch, offsets, row_of, place_of) -> None:
 
 
 GROUPED_TC05_MIN_PLACES = 128      # fewer places than this (decode rows, short portions) stay on the mma.sync tiles
-_GROUPED_TC05_ACTS = {"none": 0, "relu2": 1}
+_GROUPED_TC05_ACTS = {"none": 0, "relu2": 1, "glu_limited": 2}
 
 
 def moe_gemm_grouped_ok(a, w, out, P: int, act: str = "none") -> bool:
@@ -1622,20 +1619,20 @@ def moe_gather(a, rows, out) -> None:
     _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(rows), _ptr(out), out.stride(0), P, a.shape[0], K, _stream()), f"moe_gather(K={K})")
 
 
-def moe_gemm_tc05(a, w, out, offsets, act: str = "none", status=None) -> None:
+def moe_gemm_tc05(a, w, out, offsets, act: str = "none", status=None, limit: float = 0.0, alpha: float = 1.702) -> None:
     """The grouped product on the tcgen05 tensor cores: out[p, :] = act(a[p, :] @ w[e]^T) for the places p of expert e
     (``a`` [P, K] already in the order of the places; ``moe_gemm_grouped_ok`` says when it may be called)."""
     _cuda(a, w, out, offsets, status)
     _i32(offsets, "offsets")
     E, N, K = w.shape
     P = out.shape[0]
-    _need(a.shape == (P, K) and a.stride(1) == 1 and out.shape == (P, N) and out.stride(1) == 1 and offsets.numel() >= E + 1,
-          "moe_gemm_tc05: a [P, K], w [E, N, K], out [P, N]")
+    _need(a.shape == (P, K) and a.stride(1) == 1 and out.shape == (P, N // 2 if act == "glu_limited" else N) and out.stride(1) == 1
+          and offsets.numel() >= E + 1, "moe_gemm_tc05: a [P, K], w [E, N, K], out [P, N] (glu_limited: [P, N / 2])")
     _need(moe_gemm_grouped_ok(a, w, out, P, act), "moe_gemm_tc05: bf16, at least 128 places, K a multiple of 8, aligned rows")
     f = _fn("gemm_tc05", "si_gemm_tc05_grouped", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int,
-                                                  _c_int, _c_p, _c_p])
+                                                  _c_int, _c_f, _c_f, _c_p, _c_p])
     _check(f(_ptr(a), a.stride(0), _weight_map(w.view(E * N, K)), _ptr(out), out.stride(0), _dt(out), _ptr(offsets), P, E, N, K,
-             _GROUPED_TC05_ACTS[act], _ptr(status), _stream()), f"moe_gemm_tc05(experts={E}, N={N}, K={K})")
+             _GROUPED_TC05_ACTS[act], float(limit), float(alpha), _ptr(status), _stream()), f"moe_gemm_tc05(experts={E}, N={N}, K={K})")
 
 
 def moe_gemm_tiles(a, a_rows, w, out, offsets, act: str = "none", limit: float = 0.0, alpha: float = 1.702) -> None:
@@ -1670,7 +1667,7 @@ def moe_gemm(a, a_rows, w, out, offsets, act: str = "none", gathered=None, statu
         if a_rows is not None:
             moe_gather(a, a_rows, gathered)
             a = gathered
-        moe_gemm_tc05(a[:P], w, out, offsets, act, status)
+        moe_gemm_tc05(a[:P], w, out, offsets, act, status, limit, alpha)
     else:
         moe_gemm_tiles(a, a_rows, w, out, offsets, act, limit, alpha)
 

@@ -63,6 +63,7 @@ class StepContext:
         self.num_logit_rows = 0
         self.status = runner.status
         self.plans: Dict = {}             # per-step host-side plans of parts, cleared each step
+        self.alias: Dict[str, str] = {}   # scratch keys that stand for another buffer for the time being (set by arrangements)
         self.seq_cap: Optional[int] = None    # fixed-shape (graph) steps: sequences the shapes are for
         # device int32 views
         self.tokens = self.positions = self.row_seq = None
@@ -72,7 +73,7 @@ class StepContext:
 
     def buf(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         """A scratch tensor that lives until the same key is asked for again."""
-        return self._runner.workspace(key, shape, dtype)
+        return self._runner.workspace(self.alias.get(key, key) if self.alias else key, shape, dtype)
 
     def upload_ints(self, key: str, values: np.ndarray, capacity: Optional[int] = None) -> torch.Tensor:
         """Copy a small int32 array to a device buffer that keeps its address from step to step

@@ -14,7 +14,7 @@ import torch
 
 from ..config.base import EmbedderSpec, ModelConfig, ModelSpec
 from ..csrc import ops
-from ..parts import Block, NormedDelta, SublayerGate, embedder_class, feed_forward_class, mixer_class, norm_class, position_class
+from ..parts import Block, NormedDelta, SublayerGate, SummedDelta, embedder_class, feed_forward_class, mixer_class, norm_class, position_class
 from ..parts.linear import configure_library_gemm, linear
 from ..engine import tracing
 
@@ -193,7 +193,7 @@ class Model:
                 delta = self.blocks[i].forward(resid, delta, ctx, caches[o])
             if self._layer_hook is not None:
                 self._layer_hook(o, resid if delta is None else resid + (
-                    delta.value() if isinstance(delta, NormedDelta) else delta.float()))
+                    delta.value() if isinstance(delta, (NormedDelta, SummedDelta)) else delta.float()))
         R = ctx.num_logit_rows
         if R == 0:
             return None
@@ -208,7 +208,10 @@ class Model:
     @staticmethod
     def _stream_add(resid, delta, extra, vec) -> None:
         """``resid += delta (+ extra) (+ vec)`` in one launch; ``delta`` may be None, a tensor or a ``NormedDelta``."""
-        if isinstance(delta, NormedDelta):
+        if isinstance(delta, SummedDelta):
+            ops.add_norm(resid, delta.a)
+            ops.add_norm(resid, delta.b, extra=extra, vec=vec)
+        elif isinstance(delta, NormedDelta):
             ops.add_norm(resid, delta.x, delta_weight=delta.norm.weight, delta_eps=delta.norm.eps, delta_bias=delta.bias,
                          extra=extra, vec=vec)
         elif delta is not None or extra is not None or vec is not None:

@@ -23,7 +23,8 @@ Options beyond the reference's block, all parameters of the part:
 ``query_temperature`` ``{"coef": c, "every": n}``: the query at position p is multiplied by ``1 + c ln(floor((p + 1) / n) + 1)``
                    (applied by the attention kernels to the row's scale, in fp32).
 ``output_gate``    name of a matrix [heads * value_dim, hidden]: the heads' results are multiplied entry by entry with
-                   ``sigmoid(W_g x)`` before the output projection; its rows are stacked behind q, k, v in one product.
+                   ``sigmoid(W_g x)`` before the output projection; its rows are stacked behind q, k, v in one product, and the
+                   attention kernels apply the gate when they store their results.
 With any option but ``names`` the mixer runs the general attention kernels (``attention_general.cu`` in 32-bit,
 ``attention_flex.cu`` on the tensor cores in bfloat16) instead of the rotary ones.
 """
@@ -146,7 +147,7 @@ class Attention(Mixer):
 
     def kernel_files(self, page_size):
         if self.general:
-            return ("attention_general",) + (("activation",) if self.gate_name else ()) + (
+            return ("attention_general",) + (
                 ("gemm_f32",) if self.dtype == torch.float32 else ("attention_flex", "gemm_skinny", "gemm_rows", "gemm_tc05"))
         names = ["rope_kv"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_skinny", "gemm_rows", "gemm_tc05"])
         if not self.uses_tensor_cores():
@@ -203,16 +204,16 @@ class Attention(Mixer):
             ops.kv_store(qkv, ctx.positions, ctx.row_seq, cache.block_table, cache.k, v_cache, cache.page_size,
                          ctx.seq_slots, H, KV, hs, vs if self.own_v else 0, status=ctx.status)
         attn = ctx.buf("attn_out", (T, H * vs), self.dtype)
+        gate = qkv[:, self.gate_off:self.gate_off + H * vs] if self.gate_name else None      # applied in the attention's epilogue
         if self.uses_flex():
             flex_plan.attend(flex_plan.plan(ctx, self.device, H, KV, hs, vs, self.own_v, self.window), qkv[:, :H * hs], cache.k,
                              v_cache, cache.block_table, attn, cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale,
-                             self.window, dist_bias=self.dist_bias, status=ctx.status, slopes=self.slopes, q_temp=self.q_temp)
+                             self.window, dist_bias=self.dist_bias, status=ctx.status, slopes=self.slopes, q_temp=self.q_temp,
+                             gate=gate)
         else:
             ops.attention_general(qkv[:, :H * hs], cache.k, v_cache, cache.block_table, ctx.row_seq, ctx.positions, attn,
                                   cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale, self.window or 0,
-                                  dist_bias=self.dist_bias, status=ctx.status, slopes=self.slopes, q_temp=self.q_temp)
-        if self.gate_name:
-            ops.sigmoid_gate(attn, qkv[:, self.gate_off:self.gate_off + H * vs], attn)
+                                  dist_bias=self.dist_bias, status=ctx.status, slopes=self.slopes, q_temp=self.q_temp, gate=gate)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(attn, self.o, out, ctx.status)
         return out

@@ -91,6 +91,18 @@ class NormedDelta:
         return d * torch.rsqrt((d * d).mean(-1, keepdim=True) + self.norm.eps) * w
 
 
+@dataclass
+class SummedDelta:
+    """Two results of one block that join the residual stream together (sublayers side by side on one norm's output):
+    ``a`` and ``b`` [T, d] in the compute dtype, in buffers of their own. A norm's ``forward`` that is given one as ``delta``
+    adds both in fp32, (stream + a) + b, in the same launch as its own norm."""
+    a: torch.Tensor
+    b: torch.Tensor
+
+    def value(self) -> torch.Tensor:
+        return self.a.float() + self.b.float()
+
+
 class Part:
     # True if ``forward`` reads nothing on the host that changes from step to step: whatever depends on
     # the step comes from device tensors of ``ctx`` or is planned in ``prepare``, and nothing waits for

@@ -18,9 +18,10 @@ a learned gate (``SublayerGate``: sigmoid of a projection of the sublayer's own 
     h += delta_in;  x1 = norm1(h);  x2 = norm2(h);  h += scale * (gate1(x1) * mixer(x1) + gate2(x2) * ffn(x2))
 The add is one kernel in fp32 on the stream itself (``ops.gated_add``), so the block hands no pending delta on.
 "parallel" runs both sublayers on the output of one norm and adds both results to the stream:
-    h += delta_in;  x = norm1(h);  h += mixer(x);  return ffn(x), still to be added
-(the mixer's result joins the fp32 stream at once, in a launch of its own, so that the feed-forward may use the same scratch;
-the feed-forward's is the pending delta of the next norm, as in "pre_norm").
+    h += delta_in;  x = norm1(h);  return (mixer(x), ffn(x)), both still to be added
+What it hands on is a ``SummedDelta``: the next norm's launch adds both results in fp32 before its own statistics. While the
+feed-forward runs, the scratch key "delta" (where parts put their results) stands for a second buffer, so that the mixer's
+result stays alive beside it.
 Another arrangement (post-norm, ...) is added with ``register_arrangement`` and needs no change here.
 """
 from __future__ import annotations
@@ -30,7 +31,7 @@ from typing import Callable, Dict, Optional
 import torch
 
 from ..csrc import ops
-from .base import FeedForward, Mixer, Norm, NormedDelta, Part
+from .base import FeedForward, Mixer, Norm, NormedDelta, Part, SummedDelta
 from .linear import linear
 
 _ARRANGEMENTS: Dict[str, Callable] = {}
@@ -165,8 +166,14 @@ def parallel(block: Block, resid, delta, ctx, cache):
     a = block.mixer.forward(x, ctx, cache)
     if block.feed_forward is None:
         return a
-    ops.add_norm(resid, a)                                # fp32 sum; ``x`` is untouched and feeds the second sublayer
-    return block.feed_forward.forward(x, ctx)
+    ctx.alias["delta"] = "delta_second"                   # the feed-forward's result beside the mixer's
+    try:
+        f = block.feed_forward.forward(x, ctx)
+    finally:
+        del ctx.alias["delta"]
+    if f.data_ptr() == a.data_ptr():
+        raise ValueError("arrangement 'parallel': the mixer and the feed-forward return the same scratch buffer")
+    return SummedDelta(a, f)
 
 
 register_arrangement("parallel", parallel, capturable=True)

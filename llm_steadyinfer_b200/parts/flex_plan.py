@@ -66,12 +66,13 @@ def plan(ctx, device, H: int, KV: int, dk: int, dv: int, own_v: bool, window, sk
 
 
 def attend(pl: dict, q, k_cache, v_cache, block_table, out, page_size, seq_slots, H, KV, dk, dv, scale, window,
-           dist_bias=None, sink=None, status=None, softcap: float = 0.0, v_share: int = 1, slopes=None, q_temp=None) -> None:
+           dist_bias=None, sink=None, status=None, softcap: float = 0.0, v_share: int = 1, slopes=None, q_temp=None,
+           gate=None) -> None:
     args = (page_size, seq_slots, H, KV, dk, dv, scale, window or 0)
     if pl["dec"] is not None:
         ops.attn_flex(q, k_cache, v_cache, block_table, pl["dec"], out, *args, dist_bias=dist_bias, sink=sink,
                       nsplit=pl["nsplit"], scratch=pl["scratch"], status=status, max_rows=pl["dec_rows"], softcap=softcap,
-                      v_share=v_share, slopes=slopes, q_temp=q_temp)
+                      v_share=v_share, slopes=slopes, q_temp=q_temp, gate=gate)
     if pl["por"] is not None:
         ops.attn_flex(q, k_cache, v_cache, block_table, pl["por"], out, *args, dist_bias=dist_bias, sink=sink, status=status,
-                      softcap=softcap, v_share=v_share, slopes=slopes, q_temp=q_temp)
+                      softcap=softcap, v_share=v_share, slopes=slopes, q_temp=q_temp, gate=gate)

@@ -16,7 +16,8 @@ entries whose first rk entries also serve as the value, for prompts and decoding
 
 Long prompt portions in bfloat16 take the other way round, which costs a third of the arithmetic there (a head's
 key and value are dq + dr and dv wide instead of rk + dr and rk): the cached latents of the portion's sequence, all
-positions up to the portion's end, are copied out of the pages (``latent_gather``), expanded by two matrix products
+positions up to the portion's end (with a window: from the first position that the portion's first row still sees), are
+copied out of the pages (``latent_gather``), expanded by two matrix products
 into per-head keys [W_uk,i c | k_rot] and values W_uv,i c, and ordinary multi-head attention with the sink runs over
 them with the whole queries. Which sequences of a step go which way is decided on the host in ``prepare`` (those
 that bring at least ``EXPAND_MIN_ROWS`` rows); both ways compute the same function, up to rounding.
@@ -128,7 +129,7 @@ class LatentAttention(Mixer):
         return USE_TENSOR_CORES and self.dtype == torch.bfloat16 and ops.attn_flex_ok(self.H, 1, self.rk + self.dr, self.rk, False)
 
     def expands(self) -> bool:
-        return (self.uses_flex() and EXPAND_MIN_ROWS > 0 and self.window is None
+        return (self.uses_flex() and EXPAND_MIN_ROWS > 0
                 and ops.attn_flex_ok(self.H, self.H, self.dq + self.dr, self.dv, True))
 
     def prepare(self, ctx, cache):
@@ -153,17 +154,20 @@ class LatentAttention(Mixer):
         per_item = ops.attn_flex_tokens(self.H, self.H)
         seqs, items, total = [], [], 0
         for e, s in enumerate(chosen):
-            row0, n, keys = int(qs[s]), int(qs[s + 1] - qs[s]), int(cl[s])
-            seqs.append((s, total, keys))
+            row0, n, end = int(qs[s]), int(qs[s + 1] - qs[s]), int(cl[s])
+            # the first position that any row of the portion sees; positions count from there in the gathered rows
+            first = max(0, end - n - self.window + 1) if self.window else 0
+            keys = end - first
+            seqs.append((s, total, keys, first))
             for b in range(0, n, per_item):
                 items.append((e, row0 + b, min(per_item, n - b), keys - n + b))
             total += keys
         items.sort(key=lambda it: -(it[3] + it[2]))
-        width = max(k for _, _, k in seqs)
+        width = max(k for _, _, k, _ in seqs)
         tag = f"latent_exp_{self.H}_{self.dq}_{self.dr}_{self.dv}_{self.rk}"
         both = ctx.upload_ints(tag, np.concatenate([np.asarray(seqs, dtype=np.int32).reshape(-1),
                                                     np.asarray(items, dtype=np.int32).reshape(-1)]))
-        seqs_d, items_d = both[:3 * len(seqs)].view(-1, 3), both[3 * len(seqs):].view(-1, 4)
+        seqs_d, items_d = both[:4 * len(seqs)].view(-1, 4), both[4 * len(seqs):].view(-1, 4)
         # the expanded rows are "pages" of one key: row j of sequence e is page first_row(e) + j
         table = ctx.buf(tag + "_table", (len(seqs), width), torch.int32)
         torch.add(seqs_d[:, 1:2], torch.arange(width, dtype=torch.int32, device=self.device).view(1, -1), out=table)
@@ -222,7 +226,7 @@ class LatentAttention(Mixer):
         keys = ctx.buf("lat_keys", (n, H * (dq + dr)), self.dtype)
         ops.latent_expand_keys(plain, dense, keys, H, dq, dr, rk)
         ops.attn_flex(q_exp, keys.view(n, H, 1, dq + dr), values.view(n, H, 1, dv), ex["table"], ex["items"], attn, 1,
-                      ex["table"].shape[0], H, H, dq + dr, dv, self.scale, 0, sink=self.sink, status=ctx.status)
+                      ex["table"].shape[0], H, H, dq + dr, dv, self.scale, self.window or 0, sink=self.sink, status=ctx.status)
 
     def _attend_absorbed(self, q_full, attn, ctx, cache, skip):
         T = q_full.shape[0]

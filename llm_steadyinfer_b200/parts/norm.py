@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from ..csrc import ops
-from .base import Norm, NormedDelta, register_norm
+from .base import Norm, NormedDelta, SummedDelta, register_norm
 
 
 class RMSNorm(Norm):
@@ -51,6 +51,8 @@ class RMSNorm(Norm):
         if isinstance(delta, NormedDelta):           # the sublayer before has a norm of its own behind it
             ops.add_norm(resid, delta.x, self.weight, self.eps, out, rows=rows, delta_weight=delta.norm.weight,
                          delta_eps=delta.norm.eps, delta_bias=delta.bias)
+        elif isinstance(delta, SummedDelta):         # two sublayers side by side: both join the stream here
+            ops.add_rmsnorm(resid, delta.a, self.weight, self.eps, out, rows=rows, ahead=ahead, delta2=delta.b)
         else:
             ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows, ahead=ahead)
 

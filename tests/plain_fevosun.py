@@ -198,19 +198,27 @@ def limited_expert(h, w, pre, limit):
 
 def route(h, w, pre, top):
     """s = softmax(W_router h) over all router rows; the ``top`` largest of s + correction are chosen (the lower index on a
-    tie); the weights are their s. Returns (ids [T, top], weights [T, top])."""
+    tie); the weights are their s. Returns (ids [T, top], weights [T, top], margin [T]: by how much the last chosen row's
+    choice score lies above the first one left out, infinite where none is left out)."""
     s = torch.softmax(h @ w[pre + "router"].T, dim=-1)
     choice = s + w[pre + "correction"]
-    ids = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :top]
-    return ids, torch.gather(s, 1, ids)
+    order = torch.sort(choice, dim=-1, descending=True, stable=True)
+    ids = order.indices[:, :top]
+    if top < choice.shape[1]:
+        margin = order.values[:, top - 1] - order.values[:, top]
+    else:
+        margin = torch.full((h.shape[0],), math.inf, dtype=F64)
+    return ids, torch.gather(s, 1, ids), margin
 
 
-def routed_ff(h, w, pre, mlp):
+def routed_ff(h, w, pre, mlp, margins=None):
     """sum over the chosen e of weight_e * expert_e(h), where the last ``identity`` router rows stand for experts that
     return h itself; plus the shared expert for every row."""
     r = mlp["router"]
     E, top = int(r["experts"]), int(r["top"])
-    ids, wts = route(h, w, pre, top)
+    ids, wts, margin = route(h, w, pre, top)
+    if margins is not None:
+        margins.append(margin)
     limit = float(mlp["expert"]["limit"])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
@@ -236,9 +244,10 @@ def mixer(kind, h, w, pre, m, eps):
     raise ValueError(kind)
 
 
-def forward(cfg, w, tokens, layers_out=None):
+def forward(cfg, w, tokens, layers_out=None, margins=None):
     """Logits [T, vocab] of a whole sequence. Every layer: h = norm1(x); x <- x + mixer(h) + ff(h).
-    ``layers_out``: a list that receives the stream after every layer."""
+    ``layers_out``: a list that receives the stream after every layer; ``margins``: a list that receives every routed
+    layer's margins [T] (see ``route``)."""
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][torch.tensor(list(tokens), dtype=torch.long)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     for i, layer in enumerate(cfg["layers"]):
@@ -247,8 +256,16 @@ def forward(cfg, w, tokens, layers_out=None):
         d = mixer(layer["type"], h, w, p + "mix.", layer["mixer"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            d = d + (dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(h, w, p + "mlp.", mlp))
+            d = d + (dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(h, w, p + "mlp.", mlp, margins))
         x = x + d
         if layers_out is not None:
             layers_out.append(x.clone())
     return offset_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(cfg, w, prompt, new):
+    """``new`` tokens, each the largest logit after the sequence so far (the whole sequence computed again every time)."""
+    toks = list(prompt)
+    for _ in range(new):
+        toks.append(int(forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]

@@ -1,0 +1,602 @@
+"""Fevosun on the GPU against the plain implementation (tests/plain_fevosun.py): every mechanism alone, prompts against
+token-by-token decoding, portions down to two tokens, unequal batches with pages and slots used again, keys just inside
+and just outside every window and at page borders, the first tokens, long decoding, other sizes, and greedy generation
+through the entry point. Weights come from tests/fevosun_configs.py, which makes them so that a lost key, a window that is
+one token off, a forgotten slope, temperature, gate, correction or identity expert shows."""
+import json
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import fevosun_configs as fc
+import plain_fevosun as pf
+import replay_util as ru
+
+pytestmark = pytest.mark.gpu
+
+# A row's error: root mean square of the difference of the logits (mean taken off) over that of the plain logits.
+# In 32-bit every row is held to the limit. In bfloat16 rounding alone gives a median well below the limit with single
+# rows above it: the limit holds for the median and for all but one row in twenty, and no row may pass four times the
+# limit. A row whose router had two choice scores closer than MARGIN at the edge of its choice may choose otherwise in
+# bfloat16, which is no fault: such rows are left out there. What a cut, a batch or a page does wrong shows in 32-bit.
+LIMIT = {torch.float32: 2e-4, torch.bfloat16: 8e-2}
+MARGIN = 0.005
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["fp32", "bf16"]
+DEV = "cuda:0"
+
+
+class Plain(ru.PlainLogits):
+    """The plain logits of a request and, per position, the smallest routing margin of any layer."""
+
+    def __init__(self, folder):
+        super().__init__(folder, pf)
+        self._margins = {}
+
+    def of(self, tokens):
+        key = tuple(tokens)
+        if key not in self._cache:
+            m = []
+            self._cache[key] = pf.forward(self.cfg, self.w, tokens, margins=m)
+            self._margins[key] = torch.stack(m).min(0).values if m else torch.full((len(key),), math.inf, dtype=torch.float64)
+        return self._cache[key]
+
+    def margin(self, tokens, p):
+        self.of(tokens)
+        return self._margins[tuple(tokens)][p].item()
+
+
+CHANGES = {"dense": fc.silence_mixer, "moe": fc.silence_mixer}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("fevosun")
+    return {n: fc.write_folder(os.path.join(str(root), n), cfg, seed=41 + i, change=CHANGES.get(n))
+            for i, (n, cfg) in enumerate(fc.CONFIGS.items())}
+
+
+@pytest.fixture(scope="module")
+def plains(folders):
+    return {n: Plain(d) for n, d in folders.items()}
+
+
+def replayer(folder, name, dtype, max_tokens, max_requests=4):
+    from llm_steadyinfer_b200.engine.replay import Replayer
+    return Replayer(folder, dtype, max_tokens, page_size=fc.PAGE_SIZE[name], max_requests=max_requests)
+
+
+def row_error(row, ref):
+    d = row.to(torch.float64) - ref
+    d = d - d.mean()
+    return (d.pow(2).mean().sqrt() / ref.sub(ref.mean()).pow(2).mean().sqrt()).item()
+
+
+def check(rp, steps, reqs, plain, dtype, what):
+    worst, n, errors = 0.0, 0, []
+    hard = LIMIT[dtype] * (4 if dtype == torch.bfloat16 else 1)
+    for rid, p, row in ru.replay_in_process(rp, steps):
+        assert torch.isfinite(row).all(), f"{what}: request {rid!r} position {p}: logits are not finite"
+        if dtype == torch.bfloat16 and plain.margin(reqs[rid], p) < MARGIN:
+            continue
+        e = row_error(row, plain.of(reqs[rid])[p])
+        assert e == e and e <= hard, f"{what}: request {rid!r} position {p}: error {e:.3e} (allowed {hard:.0e})"
+        worst, n = max(worst, e), n + 1
+        errors.append(e)
+    assert n > 0
+    if dtype == torch.bfloat16:
+        errors.sort()
+        over = sum(e > LIMIT[dtype] for e in errors)
+        assert over <= max(1, n // 20), f"{what}: {over} of {n} rows above {LIMIT[dtype]:.0e}"
+        assert errors[n // 2] <= LIMIT[dtype] / 2 or n < 4, f"{what}: median error {errors[n // 2]:.3e}"
+    mgr = rp.runner.manager
+    mgr.check_invariant()
+    assert not mgr.requests
+    assert all(mgr.free_pages(g) == mgr.groups[g].pool.num_pages for g in range(len(mgr.groups)))
+    return worst
+
+
+def requests_of(name, lengths, seed=0):
+    vocab = fc.CONFIGS[name]["vocab"]
+    return {f"q{i}": ru.random_tokens(vocab, n, 1000 * seed + i) for i, n in enumerate(lengths)}
+
+
+# ---- each mechanism alone, and the layers of a whole model one by one ------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("name", ["attn", "lat1", "lat2", "dense", "moe"])
+def test_each_mechanism_alone(folders, plains, name, dtype):
+    """One-layer models of one mixer without feed-forward, or of one feed-forward beside a mixer whose output projection is
+    zero: the logits whole and token by token."""
+    reqs = requests_of(name, [1, 2, 37, 90])
+    for mode, steps in (("whole", ru.trace_whole(reqs)), ("tail", ru.trace_tail(reqs, tail=30))):
+        rp = replayer(folders[name], name, dtype, 128)
+        check(rp, steps, reqs, plains[name], dtype, f"{name}/{mode}")
+
+
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
+def test_layers_one_by_one_in_32_bit(folders, name):
+    """The residual stream after every layer against the plain one."""
+    toks = ru.random_tokens(fc.CONFIGS[name]["vocab"], 75, 5)
+    cfg, w = pf.read_model_folder(folders[name])
+    want = []
+    pf.forward(cfg, w, toks, layers_out=want)
+    rp = replayer(folders[name], name, torch.float32, 128)
+    got = {}
+    rp.runner.model.hook_layers(lambda run, resid: got.__setitem__(run, resid.double().cpu()))
+    rp.run_step([{"id": "a", "tokens": toks, "want": [len(toks) - 1]}], end=["a"])
+    assert sorted(got) == list(range(len(cfg["layers"])))
+    for run in range(len(cfg["layers"])):
+        scale = want[run].abs().max().item()
+        diff = (got[run] - want[run]).abs().max().item()
+        assert diff <= 5e-5 * scale, f"{name}: layer {run} differs by {diff:.2e} of {scale:.1f}"
+
+
+def test_every_mechanism_counts_in_the_tests_weights(folders):
+    """The plain logits change by far more than the tests' limit when a mechanism is left out of the plain implementation:
+    otherwise the comparisons above would not notice its absence in the engine."""
+    name = "mixed_a"
+    cfg, w = pf.read_model_folder(folders[name])
+    toks = ru.random_tokens(cfg["vocab"], 80, 9)
+    ref = pf.forward(cfg, w, toks)
+
+    def differs(cfg2, w2):
+        out = pf.forward(cfg2, w2, toks)
+        return max(row_error(out[i], ref[i]) for i in range(40, 80))
+
+    import copy
+    c = copy.deepcopy(cfg); c["layers"][0]["mixer"].pop("q_temp")
+    assert differs(c, w) > 50 * LIMIT[torch.float32], "query temperature"
+    c = copy.deepcopy(cfg); c["layers"][0]["mixer"]["mask"]["size"] += 1
+    assert differs(c, w) > 50 * LIMIT[torch.float32], "window of the attention"
+    c = copy.deepcopy(cfg); c["layers"][1]["mixer"]["mask"]["size"] -= 1
+    assert differs(c, w) > 50 * LIMIT[torch.float32], "window of the latent attention"
+    c = copy.deepcopy(cfg); c["layers"][1]["mixer"]["rot"].pop("scaling")
+    assert differs(c, w) > 50 * LIMIT[torch.float32], "scaling of the rotation"
+    w2 = dict(w); w2["l0.mlp.correction"] = torch.zeros_like(w["l0.mlp.correction"])
+    assert differs(cfg, w2) > 50 * LIMIT[torch.float32], "correction of the choice"
+    w2 = dict(w); w2["l0.mix.g"] = torch.zeros_like(w["l0.mix.g"])
+    assert differs(cfg, w2) > 50 * LIMIT[torch.float32], "output gate"
+    c = copy.deepcopy(cfg); c["layers"][0]["mlp"]["expert"]["limit"] = 50.0
+    assert differs(c, w) > 50 * LIMIT[torch.float32], "limit of the experts"
+    c = copy.deepcopy(cfg); c["embedding"]["scale"] = 1.0
+    assert differs(c, w) > 50 * LIMIT[torch.float32], "scale of the embedding"
+    w2 = dict(w); w2["l2.norm1"] = torch.zeros_like(w["l2.norm1"])
+    assert differs(cfg, w2) > 50 * LIMIT[torch.float32], "norm vector around zero"
+
+
+# ---- schedules ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_schedules(folders, plains, name, dtype, mode):
+    reqs = requests_of(name, [1, 3, 19, 64, 65, 130, 201], seed=1)
+    longest = ru.round64(max(len(t) for t in reqs.values()))
+    if mode == "whole":
+        steps, max_tokens = ru.trace_whole(reqs), longest
+    elif mode == "tail":
+        steps, max_tokens = ru.trace_tail(reqs, tail=40), longest
+    elif mode == "portions":
+        steps, max_tokens = ru.trace_portions(reqs, sizes=(2, 17, 3, 2, 31, 5, 64, 2, 9, 1, 40)), longest
+    else:
+        max_tokens = longest + 128                       # two or three live at a time: pages and slots come again
+        steps = ru.trace_mixed(reqs, max_tokens, seed=3, max_live=3)
+    rp = replayer(folders[name], name, dtype, max_tokens, max_requests=3)
+    worst = check(rp, steps, reqs, plains[name], dtype, f"{name}/{mode}")
+    print(f"{name} {mode} {dtype}: worst row error {worst:.2e}")
+
+
+def test_prompt_equals_token_by_token_in_32_bit(folders):
+    """The same request whole, one token a step, and in portions of two: the logits agree far below the distance to the
+    plain implementation (the kernels differ between the three, the function does not)."""
+    name = "mixed_a"
+    toks = ru.random_tokens(fc.CONFIGS[name]["vocab"], 70, 12)
+    reqs = {"a": toks}
+    runs = []
+    for steps in (ru.trace_whole(reqs), ru.trace_portions(reqs, sizes=(1,)), ru.trace_portions(reqs, sizes=(2,))):
+        rp = replayer(folders[name], name, torch.float32, 128)
+        runs.append(torch.stack([row for _, _, row in ru.replay_in_process(rp, steps)]).double())
+    for other in runs[1:]:
+        e = max(row_error(other[i], runs[0][i]) for i in range(len(toks)))
+        assert e < 2e-5, f"prompt and steps differ by {e:.2e}"
+
+
+def test_batch_equals_alone_and_slots_come_again(folders, plains):
+    """Unequal requests in one batch against each alone, with two request slots for five requests: every slot and page is
+    used again, and the keys that the request before left there must not show."""
+    name, dtype = "mixed_a", torch.float32
+    reqs = requests_of(name, [70, 9, 33, 2, 51], seed=2)
+    steps = ru.trace_mixed(reqs, 192, seed=9, max_live=2, prompt_frac=0.5)
+    rp = replayer(folders[name], name, dtype, 192, max_requests=2)
+    check(rp, steps, reqs, plains[name], dtype, "two slots")
+    again = dict(reversed(list(reqs.items())))
+    check(rp, ru.trace_mixed(again, 192, seed=10, max_live=2, prompt_frac=0.3), again, plains[name], dtype, "two slots again")
+
+
+def test_long_decoding(folders, plains):
+    """A short prompt, then 300 tokens one by one: every window passes wholly over decoded tokens, pages behind the
+    windows go back to the pool and the query temperature changes many times."""
+    name = "mixed_a"
+    reqs = requests_of(name, [310], seed=3)
+    for dtype in DTYPES:
+        rp = replayer(folders[name], name, dtype, 320)
+        check(rp, ru.trace_tail(reqs, tail=300), reqs, plains[name], dtype, "long decoding")
+
+
+def test_first_tokens(folders, plains):
+    """Positions 0, 1, 2 alone and as the start of portions: a softmax over one key, a rotation by angle zero, a
+    temperature of one, windows that are not full yet."""
+    name = "mixed_b"
+    reqs = requests_of(name, [1, 2, 3, 5], seed=4)
+    for dtype in DTYPES:
+        for sizes in ((1,), (2, 1), (1, 2)):
+            rp = replayer(folders[name], name, dtype, 64)
+            check(rp, ru.trace_portions(reqs, sizes=sizes), reqs, plains[name], dtype, f"first tokens {sizes}")
+
+
+@pytest.mark.parametrize("kind", ["attention", "latent"])
+def test_a_key_at_the_window_edge_decides(tmp_path, kind):
+    """One layer with sharp attention: the logits of late rows depend on the token that lies window - 1 back and not on the
+    one that lies window back, in the plain implementation; the engine must follow in prompts, in portions cut at the edge
+    and in single tokens."""
+    window = 21
+    if kind == "attention":
+        cfg = fc.model(120, 64, 1e-5, [fc.layer(fc.attn(4, 2, 16, window=window, coef=0.6, every=10, scale=0.6))])
+    else:
+        cfg = fc.model(120, 64, 1e-5, [fc.layer(fc.latent(4, 16, 8, 8, 24, window=window, scale=0.5))])
+    folder = fc.write_folder(str(tmp_path / kind), cfg, 6)
+    plain = Plain(folder)
+    n = 90
+    a = ru.random_tokens(120, n, 78)
+    inside, outside = list(a), list(a)
+    inside[n - window] = (a[n - window] + 31) % 120               # the last row still sees this place
+    outside[n - window - 1] = (a[n - window - 1] + 31) % 120      # and not this one
+    assert row_error(plain.of(inside)[-1], plain.of(a)[-1]) > 50 * LIMIT[torch.float32], "the key inside the window does not count"
+    assert row_error(plain.of(outside)[-1], plain.of(a)[-1]) < 1e-9, "the key outside the window counts"
+    name = "attn" if kind == "attention" else "lat1"
+    for dtype in DTYPES:
+        reqs = {"a": a, "in": inside, "out": outside}
+        check(replayer(folder, name, dtype, 128), ru.trace_portions(reqs, sizes=(n - window - 1, 1, 2, window - 3, 1)), reqs, plain, dtype, "window edge, portions")
+        check(replayer(folder, name, dtype, 128), ru.trace_tail(reqs, tail=window + 5), reqs, plain, dtype, "window edge, decoding")
+
+
+def test_other_sizes_where_the_usual_ones_coincide(tmp_path, plains):
+    """Sizes that a model may make equal or one: a single head, a single expert with every choice an identity expert or
+    none, a temperature that changes every token, a coefficient of zero."""
+    cfg = fc.model(64, 32, 1e-5, [
+        fc.layer(fc.attn(1, 1, 12, window=3, coef=0.0, every=1), fc.moe(8, 1, 1, 2, limit=0.7)),
+        fc.layer(fc.latent(1, 8, 2, 4, 8, window=2, q_rank=4), fc.moe(12, 2, 0, 1, limit=1.1, shared=4)),
+        fc.layer(fc.attn(2, 2, 4, window=200, coef=2.0, every=1), None),
+    ])
+    folder = fc.write_folder(str(tmp_path / "small"), cfg, 8)
+    plain = Plain(folder)
+    reqs = {f"q{i}": ru.random_tokens(64, n, 50 + i) for i, n in enumerate([1, 2, 7, 40])}
+    for dtype in DTYPES:
+        check(replayer(folder, "odd", dtype, 64), ru.trace_portions(reqs, sizes=(3, 2, 1, 9)), reqs, plain, dtype, "small sizes")
+
+
+# ---- kernels ----------------------------------------------------------------------------------------------
+
+def _paged(rows, page_size, perm_seed):
+    """rows [n, heads, d] into a shuffled page pool; returns (cache [pages, heads, page_size, d], table [1, blocks])."""
+    n, KV, d = rows.shape
+    blocks = -(-n // page_size)
+    g = torch.Generator().manual_seed(perm_seed)
+    pages = torch.randperm(blocks + 3, generator=g)[:blocks]
+    cache = torch.zeros(blocks + 3, KV, page_size, d, dtype=rows.dtype)
+    for j in range(n):
+        cache[pages[j // page_size], :, j % page_size] = rows[j]
+    return cache, pages.to(torch.int32).view(1, -1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("H,G,dk,dv,window,every", [(4, 2, 24, 24, 37, 16), (8, 2, 64, 64, 100, 128), (3, 1, 10, 6, 64, 7), (6, 6, 16, 8, None, 1),
+                                                        (16, 4, 32, 32, 1, 50)])
+def test_attention_with_slopes_temperature_gate_and_keys_as_values(H, G, dk, dv, window, every, dtype):
+    """Queries built so that one key carries nearly all of a head's weight without the slopes: keys at page borders, a key far
+    back, the key just inside the window and the one just outside. The values are the keys' first entries. Rows run as a
+    prompt and once more one by one; the tensor-core kernel too where the sizes allow it."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(3 + H)
+    n, ps = 330, 16
+    ratio = H // G
+    k = torch.randn(n, G, dk) * 0.3
+    q = torch.randn(n, H, dk) * 0.3
+    w = window or n
+    dists = sorted({0, 1, w - 2, w - 1, w, w + 1, 15, 16, 17, 31, 32, 33, 250, 300} & set(range(n)))
+    for e, dist in enumerate(dists):                      # query i looks hard at the key `dist` back
+        i = n - 1 - e
+        if i - dist < 0:
+            continue
+        k[i - dist] = k[i - dist] / k[i - dist].norm(dim=-1, keepdim=True) * 6.0
+        for h in range(H):
+            q[i, h] = k[i - dist, h // ratio] * (1.5 if h % 2 else 1.0)
+    q, k = (t.to(dtype).double() for t in (q, k))
+    scale, coef = 0.5, 0.4
+    gate = torch.randn(n, H * dv).to(dtype)
+    slopes = pf.distance_slopes(H)
+    pos = torch.arange(n)
+    temp = pf.query_temperature(pos, coef, float(every))
+    kh = k.repeat_interleave(ratio, dim=1)
+    s = torch.einsum("ihd,jhd->hij", q * temp.view(n, 1, 1), kh) * scale
+    s = s - slopes.view(H, 1, 1) * (pos.view(-1, 1) - pos.view(1, -1)).double().unsqueeze(0)
+
+    def result(win):
+        o = pf.softmax_attend(s, pf.window_mask(n, win), kh[:, :, :dv].permute(1, 0, 2)).reshape(n, H * dv)
+        return o * torch.sigmoid(gate.double())
+
+    want = result(window)
+    if window and window in dists:                        # the key just outside would have dominated
+        i = n - 1 - dists.index(window)
+        assert (result(window + 1)[i] - want[i]).abs().max() > 0.05
+    qd = q.reshape(n, H * dk).to(dtype).to(DEV)
+    kc, table = _paged(k.to(dtype), ps, 3)
+    kc, table = kc.to(DEV), table.to(DEV)
+    seqs, posd = torch.zeros(n, dtype=torch.int32, device=DEV), torch.arange(n, dtype=torch.int32, device=DEV)
+    slopes_d, gate_d = slopes.float().to(DEV), gate.to(DEV)
+    limit = 1e-4 if dtype == torch.float32 else 4e-2
+    extra = dict(slopes=slopes_d, q_temp=(coef, every))
+
+    out = torch.zeros(n, H * dv, dtype=dtype, device=DEV)
+    ops.attention_general(qd, kc, None, table, seqs, posd, out, ps, 1, H, G, dk, dv, scale, window or 0, gate=gate_d, **extra)
+    diff = (out.double().cpu() - want).abs().max().item()
+    assert diff <= limit, f"prompt rows differ by {diff:.2e}"
+    last = 40
+    one = torch.zeros(last, H * dv, dtype=dtype, device=DEV)
+    for r in range(n - last, n):                          # single rows, as decoding brings them
+        ops.attention_general(qd[r:r + 1], kc, None, table, seqs[:1], posd[r:r + 1], one[r - n + last:r - n + last + 1], ps, 1, H, G, dk,
+                              dv, scale, window or 0, gate=gate_d[r:r + 1], **extra)
+    diff = (one.double().cpu() - want[n - last:]).abs().max().item()
+    assert diff <= limit, f"single rows differ by {diff:.2e}"
+    if dtype == torch.bfloat16 and ops.attn_flex_ok(H, G, dk, dv, False):
+        per = ops.attn_flex_tokens(H, G)
+        items = torch.tensor([(0, b, min(per, n - b), b) for b in range(0, n, per)], dtype=torch.int32, device=DEV)
+        out2 = torch.zeros(n, H * dv, dtype=dtype, device=DEV)
+        ops.attn_flex(qd, kc, None, table, items, out2, ps, 1, H, G, dk, dv, scale, window or 0, gate=gate_d, **extra)
+        diff = (out2.double().cpu() - want).abs().max().item()
+        assert diff <= limit, f"tensor cores, prompt rows: {diff:.2e}"
+        for nsplit in (1, 3):                             # single rows, their keys whole and cut into shares
+            one2 = torch.zeros(last, H * dv, dtype=dtype, device=DEV)
+            for r in range(n - last, n):
+                it = torch.tensor([(0, 0, 1, r)], dtype=torch.int32, device=DEV)
+                scratch = torch.zeros(ops.attn_flex_scratch_floats(1, H, G, dv, nsplit), dtype=torch.float32, device=DEV) if nsplit > 1 else None
+                ops.attn_flex(qd[r:r + 1], kc, None, table, it, one2[r - n + last:r - n + last + 1], ps, 1, H, G, dk, dv, scale, window or 0,
+                              gate=gate_d[r:r + 1], nsplit=nsplit, scratch=scratch, max_rows=H // G, **extra)
+            diff = (one2.double().cpu() - want[n - last:]).abs().max().item()
+            assert diff <= limit, f"tensor cores, single rows in {nsplit} shares: {diff:.2e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("scores", ["softmax", "sigmoid"])
+def test_router_with_a_bias_on_the_choice(scores, dtype):
+    """The chosen rows are the largest of score + bias, the weights the scores alone; without a bias the choice is as before."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(5)
+    T, d, E, top = 50, 40, 11, 4
+    x = torch.randn(T, d).to(dtype)
+    w = (torch.randn(E, d) * 0.4).to(dtype)
+    bias = torch.randn(E) * 0.3
+    z = x.double() @ w.double().T
+    s = torch.softmax(z, -1) if scores == "softmax" else torch.sigmoid(z)
+    for b in (bias, None):
+        choice = s + (b.double() if b is not None else 0.0)
+        order = torch.sort(choice, dim=-1, descending=True, stable=True)
+        ids = torch.zeros(T, top, dtype=torch.int32, device=DEV)
+        wts = torch.zeros(T, top, dtype=torch.float32, device=DEV)
+        ops.moe_route(x.to(DEV), w.to(DEV), E, top, 1.0, ids, wts, None, scores=scores, choice_bias=None if b is None else b.to(DEV))
+        clear = (order.values[:, top - 1] - order.values[:, top]) > 1e-3            # rows without a close call
+        assert clear.sum() > T // 2
+        got = ids.cpu().long()
+        assert (got[clear] == order.indices[:, :top][clear]).all()
+        want_w = torch.gather(s, 1, got)
+        assert (wts.cpu().double() - want_w).abs().max() < (1e-5 if dtype == torch.float32 else 2e-2)
+    if scores == "softmax":
+        assert (torch.sort(s + bias.double(), -1, descending=True).indices[:, :top] != torch.sort(s, -1, descending=True).indices[:, :top]).any()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("T,d,F,E,I,top", [(9, 48, 24, 5, 2, 3), (300, 64, 40, 4, 3, 2), (33, 50, 18, 3, 0, 3)])
+def test_grouped_products_with_limited_gates_and_identity_experts(T, d, F, E, I, top, dtype):
+    """Route, plan, both grouped products and the combination against the plain sums: few places (tiles of 16), many places
+    (the tcgen05 grouped product in bfloat16), sizes that are no multiple of 8, no identity experts."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(T)
+    limit, alpha = 0.8, 1.702
+    x = torch.randn(T, d).to(dtype)
+    router = (torch.randn(E + I, d) * 0.4).to(dtype)
+    gate_w, up_w = (torch.randn(E, F, d) / math.sqrt(d) * 1.4).to(dtype), (torch.randn(E, F, d) / math.sqrt(d) * 1.4).to(dtype)
+    down_w = (torch.randn(E, d, F) / math.sqrt(F)).to(dtype)
+    ids = torch.zeros(T, top, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(T, top, dtype=torch.float32, device=DEV)
+    xd = x.to(DEV)
+    ops.moe_route(xd, router.to(DEV), E + I, top, 1.0, ids, wts, None, scores="softmax")
+    P = T * top
+    scratch = torch.zeros(ops.moe_plan_ints(P, E + I), dtype=torch.int32, device=DEV)
+    offsets = torch.zeros(E + I + 1, dtype=torch.int32, device=DEV)
+    row_of = torch.zeros(P, dtype=torch.int32, device=DEV)
+    place_of = torch.zeros(T, top, dtype=torch.int32, device=DEV)
+    ops.moe_plan(ids, E + I, scratch, offsets, row_of, place_of)
+    stacked = torch.stack([gate_w, up_w], 2).reshape(E, 2 * F, d).contiguous().to(DEV)       # gate and up rows in turn
+    act = torch.zeros(P, F, dtype=dtype, device=DEV)
+    gathered = torch.zeros(P, d, dtype=dtype, device=DEV) if ops.moe_gemm_grouped_ok(xd, stacked, act, P, "glu_limited") else None
+    assert (gathered is not None) == (dtype == torch.bfloat16 and P >= 128 and d % 8 == 0)
+    ops.moe_gemm(xd, row_of, stacked, act, offsets, act="glu_limited", gathered=gathered, limit=limit, alpha=alpha)
+    y = torch.zeros(P, d, dtype=torch.float32, device=DEV)
+    ops.moe_gemm(act, None, down_w.to(DEV), y, offsets)
+    out = torch.zeros(T, d, dtype=dtype, device=DEV)
+    ops.moe_combine(y, place_of, wts, out, ids=ids if I else None, real=E, x=xd if I else None)
+    want = torch.zeros(T, d, dtype=torch.float64)
+    idc, wc = ids.cpu().long(), wts.cpu().double()
+    for t in range(T):
+        for c in range(top):
+            e = int(idc[t, c])
+            if e >= E:
+                yv = x[t].double()
+            else:
+                g = torch.clamp(gate_w[e].double() @ x[t].double(), max=limit)
+                u = torch.clamp(up_w[e].double() @ x[t].double(), -limit, limit)
+                yv = down_w[e].double() @ (g * torch.sigmoid(alpha * g) * (u + 1.0))
+            want[t] += wc[t, c] * yv
+    if I:
+        assert (idc >= E).any(), "no identity expert was chosen in this test"
+    diff = (out.double().cpu() - want).abs().max().item()
+    assert diff <= (1e-4 if dtype == torch.float32 else 3e-2), f"routed sum differs by {diff:.2e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("hidden", [64, 70, 4096])
+def test_two_results_join_the_stream_in_one_norm(hidden, dtype):
+    """resid += a + b in fp32 and the norm of the sum, with and without chosen rows."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(hidden)
+    T = 13
+    resid = torch.randn(T, hidden, dtype=torch.float32, device=DEV) * 3
+    a, b = torch.randn(T, hidden, device=DEV).to(dtype), torch.randn(T, hidden, device=DEV).to(dtype)
+    w = (1.0 + 0.1 * torch.randn(hidden, device=DEV)).float()
+    want_sum = resid.double() + a.double() + b.double()
+    want = want_sum / torch.sqrt((want_sum * want_sum).mean(-1, keepdim=True) + 1e-5) * w.double()
+    rows = torch.tensor([12, 0, 5], dtype=torch.int32, device=DEV)
+    picked = torch.zeros(3, hidden, dtype=dtype, device=DEV)
+    before = resid.clone()
+    ops.add_rmsnorm(resid, a, w, 1e-5, picked, rows=rows, delta2=b)
+    assert torch.equal(resid, before)
+    out = torch.zeros(T, hidden, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(resid, a, w, 1e-5, out, delta2=b)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (resid.double() - want_sum).abs().max() < 1e-5
+    assert (out.double() - want).abs().max() < tol
+    assert (picked.double() - want[rows.long()]).abs().max() < tol
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_latent_rotation_pairs_and_magnitude(interleaved):
+    """The kernel between the latent attention's projections and its attention: norm of the latent, rotation of the shared key
+    part and of the queries' rotated parts in either pairing, cosines and sines times a magnitude."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(11)
+    T, H, dq, dr, rk, ps, mag = 21, 3, 8, 6, 10, 4, 1.07
+    kv = torch.randn(T, rk + dr, device=DEV)
+    q = torch.randn(T, H * (dq + dr), device=DEV)
+    q_full = torch.zeros(T, H * (rk + dr), device=DEV)
+    norm_w = (1.0 + 0.2 * torch.randn(rk, device=DEV)).float()
+    freqs = torch.tensor([0.9, 0.31, 0.05], dtype=torch.float32, device=DEV)
+    pos = torch.arange(100, 100 + T, dtype=torch.int32, device=DEV)
+    seqs = torch.zeros(T, dtype=torch.int32, device=DEV)
+    blocks = -(-(100 + T) // ps)
+    table = torch.arange(blocks, dtype=torch.int32, device=DEV).flip(0).view(1, -1).contiguous()
+    cache = torch.zeros(blocks, 1, ps, rk + dr, device=DEV)
+    ops.latent_prepare(kv, q, q_full, norm_w, 1e-5, freqs, dr, pos, seqs, table, cache, ps, 1, H, dq, dr, rk, interleaved=interleaved,
+                       rot_scale=mag)
+    p64 = pos.cpu().long()
+    f64 = freqs.cpu().double()
+    want_k = pf.rotate(kv[:, rk:].cpu().double().view(T, 1, dr), p64, f64, mag, interleaved)[:, 0]
+    want_c = pf.plain_norm(kv[:, :rk].cpu().double(), norm_w.cpu().double(), 1e-5)
+    want_q = pf.rotate(q.cpu().double().view(T, H, dq + dr)[:, :, dq:], p64, f64, mag, interleaved)
+    for t in range(T):
+        p = 100 + t
+        row = cache[table[0, p // ps], 0, p % ps].cpu().double()
+        assert (row[:rk] - want_c[t]).abs().max() < 1e-5 and (row[rk:] - want_k[t]).abs().max() < 1e-4
+    got_q = q_full.cpu().double().view(T, H, rk + dr)[:, :, rk:]
+    assert (got_q - want_q).abs().max() < 1e-4
+
+
+# ---- the entry point ----------------------------------------------------------------------------------------
+
+def greedy(cfg, w, prompt, new):
+    """``new`` greedy tokens of the plain implementation, and the smallest gap between the two best logits on the way."""
+    toks, gap = list(prompt), math.inf
+    for _ in range(new):
+        logits = pf.forward(cfg, w, toks)[-1]
+        top2 = torch.topk(logits, 2).values
+        gap = min(gap, (top2[0] - top2[1]).item())
+        toks.append(int(logits.argmax()))
+    return toks[len(prompt):], gap
+
+
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b"])
+def test_greedy_generation_through_the_entry_point(folders, name):
+    """Greedy tokens through LLM (scheduler, sampler, graphs and steps launched ahead) equal the plain implementation's
+    in 32-bit; bfloat16 runs and mostly agrees."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    cfg, w = pf.read_model_folder(folders[name])
+    prompts = [ru.random_tokens(cfg["vocab"], n, 50 + n) for n in (5, 23, 1, 40)]
+    both = [greedy(cfg, w, p, 12) for p in prompts]
+    want = [b[0] for b in both]
+    assert min(b[1] for b in both) > 1e-3, "the test's prompts meet a close call between two tokens"
+    for dtype in ("float32", "bfloat16"):
+        for graphs in (True, False):
+            llm = LLM(folders[name], dtype=dtype, max_batch=3, max_seq_len=64, max_gen_len=12, block_size=fc.PAGE_SIZE[name],
+                      max_num_batched_tokens=32, use_cuda_graph=graphs, async_decode=graphs)
+            got = [g.token_ids for g in llm.generate(prompts, SamplingParams(ignore_eos=True))]
+            if dtype == "float32":
+                assert got == want, f"{name} graphs={graphs}: {got} != {want}"
+            else:
+                same = sum(a == b for g, x in zip(got, want) for a, b in zip(g, x))
+                assert same >= 24, f"{name} bf16: only {same} of 48 tokens agree"
+            if graphs:
+                assert llm.runner.graphs_available() and llm.stats["graph_steps"] > 0
+
+
+def test_preemption_recomputes_from_the_start(folders):
+    """A pool too small for all requests: some are cut back and computed again; with windows nothing of a cut request can
+    be kept, and the tokens still equal the plain implementation's."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    name = "mixed_a"
+    cfg, w = pf.read_model_folder(folders[name])
+    prompts = [ru.random_tokens(cfg["vocab"], n, 90 + n) for n in (30, 28, 26)]
+    want = [greedy(cfg, w, p, 20)[0] for p in prompts]
+    llm = LLM(folders[name], dtype="float32", max_batch=3, max_seq_len=64, max_gen_len=20, block_size=8, num_blocks=14,
+              max_num_batched_tokens=64)
+    res = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [r.token_ids for r in res] == want
+
+
+def test_trace_program_replays_a_mixed_trace(folders, plains, tmp_path):
+    """``bin/trace_run`` as a program: a mixed trace in 32-bit, its files and its "done" lines."""
+    name = "mixed_a"
+    reqs = requests_of(name, [40, 3, 90, 17, 66], seed=7)
+    steps = ru.trace_mixed(reqs, 256, seed=1, max_live=3)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders[name], "--dtype", "float32",
+                           "--out", str(out), "--max-tokens", "256", "--page-size", str(fc.PAGE_SIZE[name])],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    pos, vocab = {}, fc.CONFIGS[name]["vocab"]
+    for rec in steps:
+        wanted = sum(len(e["want"]) for e in rec["entries"])
+        rows = None
+        if wanted:
+            rows = torch.from_file(str(out / f"{rec['step']}.f32"), size=wanted * vocab, dtype=torch.float32).view(wanted, vocab)
+        r = 0
+        for e in rec["entries"]:
+            base = pos.get(e["id"], 0)
+            for wpos in e["want"]:
+                assert row_error(rows[r], plains[name].of(reqs[e["id"]])[base + wpos]) <= LIMIT[torch.float32]
+                r += 1
+            pos[e["id"]] = base + len(e["tokens"])
+
+
+def test_command_line_serves_the_design(folders, tmp_path):
+    """The serving program on a Fevosun folder: requests of random lengths arriving over time, sampling, a pool that is
+    used again; and once more on random weights drawn from a configuration file."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "m.json"
+    common = ["--num-requests", "12", "--max-batch", "4", "--max-gen", "10", "--prompt-len-dist", "lognormal:30,0.7,2,90",
+              "--output-len-dist", "lognormal:6,0.5,1,10", "--request-rate", "300", "--temperature", "0.8", "--top-p", "0.9",
+              "--ignore-eos", "--kv-block-size", "8", "--num-kv-blocks", "60", "--max-num-batched-tokens", "40",
+              "--max-model-len", "128", "--output-json", str(out)]
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(fc.clean(fc.MIXED_A)))           # every size is in the file: the query latent's too
+    for source in (["--checkpoint", folders["mixed_a"]], ["--model-config", str(cfg_file)]):
+        proc = subprocess.run([sys.executable, os.path.join(root, "bin", "offline_batch_benchmark"), *source, *common],
+                              capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-3000:]
+        m = json.loads(out.read_text())[0]
+        assert m["completed"] == 12 and m["rejected"] == 0 and m["output_tokens"] > 12 and m["output_tps"] > 0
