@@ -99,6 +99,8 @@ class FevosunConfig(ModelConfig):
                 qt = _sub(mx, "q_temp", where + "mixer.", optional=True)
                 if qt is not None:
                     _keyed(lambda: read_key(qt, "coef", float), where + "mixer.q_temp.")
+                    if isinstance(qt.get("every"), float) and qt["every"].is_integer():
+                        qt["every"] = int(qt["every"])              # a whole number written with a point
                     _keyed(lambda: read_key(qt, "every", int, positive=True), where + "mixer.q_temp.")
             else:
                 rot = _sub(mx, "rot", where + "mixer.")

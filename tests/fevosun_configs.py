@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 
-def attn(heads, kv, dim, window=None, coef=0.5, every=16, scale=None, vdim=None):
+def attn(heads, kv, dim, window=None, coef=0.6, every=16, scale=None, vdim=None):
     d = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim if vdim is None else vdim,
          "scale": scale if scale is not None else dim ** -0.5}
     if window is not None:
@@ -83,7 +83,7 @@ ONLY_MOE = model(200, 64, 1e-5, [layer(attn(2, 1, 8, window=5), moe(40, 5, 3, 3,
 # all of it, every layer different
 MIXED_A = model(331, 96, 1e-5, [
     layer(attn(4, 2, 24, window=19, coef=0.4, every=7), moe(48, 6, 2, 2, limit=1.0, shared=72)),
-    layer(latent(4, 16, 8, 24, 40, window=50, base=50000.0, scaling=YARN), dense(136)),
+    layer(latent(4, 16, 8, 24, 40, window=50, base=30000.0, scaling=YARN), dense(136)),
     layer(latent(3, 24, 16, 8, 32, window=13, q_rank=24), moe(32, 5, 0, 5, limit=0.6)),
     layer(attn(6, 6, 8, window=1, coef=1.0, every=3), None),
     layer(attn(3, 1, 16, window=None, every=None, scale=0.3), moe(64, 7, 1, 1, limit=2.0, shared=16, shared_limit=0.5)),
@@ -91,8 +91,8 @@ MIXED_A = model(331, 96, 1e-5, [
 # sizes in multiples of 16 (what the tensor-core kernels take), more heads, wider
 MIXED_B = model(500, 256, 2e-6, [
     layer(latent(8, 32, 16, 40, 80, window=72, base=250.0, scaling={"factor": 8.0, "original": 32, "fast": 4.0, "slow": 2.0}),
-          moe(128, 8, 3, 2, limit=1.5, shared=128, shared_limit=2.0)),
-    layer(attn(8, 4, 32, window=33, coef=0.5, every=32), dense(384)),
+          moe(128, 8, 3, 2, limit=1.3, shared=128, shared_limit=1.8)),
+    layer(attn(8, 4, 32, window=33, coef=0.45, every=32), dense(384)),
     layer(latent(4, 64, 32, 32, 96, window=40, q_rank=48, with_rank=False), moe(64, 16, 2, 4, limit=1.0, shared=192)),
     layer(attn(16, 4, 16, window=130, coef=0.25, every=50), moe(256, 4, 4, 8, limit=1.2)),
 ], embed_scale=3.5)

@@ -295,7 +295,7 @@ def _paged(rows, page_size, perm_seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("H,G,dk,dv,window,every", [(4, 2, 24, 24, 37, 16), (8, 2, 64, 64, 100, 128), (3, 1, 10, 6, 64, 7), (6, 6, 16, 8, None, 1),
+@pytest.mark.parametrize("H,G,dk,dv,window,every", [(4, 2, 24, 24, 37, 16), (8, 2, 48, 48, 100, 96), (3, 1, 10, 6, 64, 7), (6, 6, 16, 8, None, 1),
                                                         (16, 4, 32, 32, 1, 50)])
 def test_attention_with_slopes_temperature_gate_and_keys_as_values(H, G, dk, dv, window, every, dtype):
     """Queries built so that one key carries nearly all of a head's weight without the slopes: keys at page borders, a key far

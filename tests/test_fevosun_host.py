@@ -116,7 +116,7 @@ def test_what_the_parts_make_of_their_weights(tmp_path):
     assert torch.allclose(att.slopes.double(), pf.distance_slopes(4), rtol=1e-7) and att.q_temp == (0.4, 7)
     assert att.qkv.shape[0] == att.proj_cols == 4 * 24 + 2 * 24 + 4 * 24 and att.gate_off == 144
     lat = model.blocks[1].mixer
-    f, mag = pf.rotary_frequencies(8, 50000.0, fc.YARN)
+    f, mag = pf.rotary_frequencies(8, 30000.0, fc.YARN)
     assert torch.allclose(lat.inv_freq.double(), f, rtol=1e-6) and abs(lat.rot_scale - mag) < 1e-12 and lat.q_rank is None
     ff = model.blocks[0].feed_forward
     assert ff.routes == 8 and ff.w_up.shape == (6, 96, 96)
