@@ -63,10 +63,19 @@ __device__ __forceinline__ bf16* half_ptr(bf16* base, int row, int chunk) {
   return base + (size_t)(chunk >> 3) * (NROWS * 64) + (size_t)row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
 }
 
-template <int NH>
+// What the extended form (EXT) adds to a score and to the result, all fp32 arithmetic in the softmax threads:
+//   score(i, j) = scale * t(i) * q.k - slope[h] * (i - j),  t(i) = 1 + qt_coef * ln(floor((i + 1) / qt_every) + 1)  (qt_every 0: t = 1)
+//   result(i, h, d) *= sigmoid(gate[i, h * hs + d])   (gate null: none)
+struct AttnExtras {
+  const float* slopes;                           // fp32 [H] or nullptr
+  float qt_coef; int qt_every;
+  const bf16* gate; long long gate_stride;       // rows 16-byte aligned
+};
+
+template <int NH, bool EXT>
 __global__ void __launch_bounds__(320)
 attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
-                         const __grid_constant__ CUtensorMap vmap, int log2_page) {
+                         const __grid_constant__ CUtensorMap vmap, int log2_page, const AttnExtras x) {
   constexpr int BM = 128, BN = 128, HS = NH * 64, STAGES = 2;
   constexpr int TILE = NH * BN * 64;                 // elements of a K (or V) tile: NH halves of [128][64]
   constexpr int TM_S = 0, TM_O = 2 * BN;             // tensor-memory columns: S of tile q at TM_S + q*BN, O at TM_O + q*HS
@@ -294,6 +303,14 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
     const unsigned ts = tmem + lane_base + TM_S + q * BN, to = tmem + lane_base + TM_O + q * HS;
     float m = -INFINITY, l = 0.f;                    // base of the exponentials (log2 domain), the row's sum
     bool alive = true;
+    // EXT: the row's own scale (its query temperature) and its head's slope, base 2; the scores then carry scale and
+    // penalty before the maximum is taken, and `sc` below is one
+    float row_scale = p.scale_log2, sl2 = 0.f;
+    if (EXT) {
+      if (x.qt_every > 0 && pos >= 0) row_scale *= 1.f + x.qt_coef * logf((float)((pos + 1) / x.qt_every + 1));
+      if (x.slopes) sl2 = x.slopes[g * p.G + (hh < p.G ? hh : 0)] * 1.4426950408889634f;
+    }
+    const float sc = EXT ? 1.f : p.scale_log2;
     for (int t = 0; t < ntiles; ++t) {
       const int j0 = kv_begin + t * BN;
       alive = mbar_wait_warp(&s_full[q], (unsigned)(t & 1));
@@ -311,6 +328,11 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
           if (j < lo || j > pos) s[i] = -INFINITY;
         }
       }
+      if (EXT) {                                           // masked scores stay -inf
+        const float c0 = sl2 * (float)(j0 - pos);
+#pragma unroll
+        for (int i = 0; i < BN; ++i) s[i] = fmaf(s[i], row_scale, fmaf(sl2, (float)i, c0));
+      }
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #if SI_ATTN_PACKED
 #pragma unroll
@@ -326,7 +348,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
       }
 #endif
       // the scale is positive, so the maximum may be taken before it
-      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sc;
       // raise the base only when the maximum has outgrown it by 2^8; then O and l are rescaled. S being
       // complete, so is every earlier product into O.
       float factor = 1.f;
@@ -346,7 +368,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
 #if SI_ATTN_PACKED
       // scale, subtraction of the base and the row's sum two scores at a time (fma.rn.f32x2, add.rn.f32x2: the
       // same roundings as the single instructions, half as many of them)
-      const unsigned long long sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nb2 = pack_f32x2(-base, -base);
+      const unsigned long long sc2 = pack_f32x2(sc, sc), nb2 = pack_f32x2(-base, -base);
       unsigned long long sum2[2] = {0ull, 0ull};
 #pragma unroll
       for (int b = 0; b < BN / 64; ++b) {
@@ -381,7 +403,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
         for (int i = 0; i < 64; i += 4) {
 #pragma unroll
           for (int w = 0; w < 4; ++w) {
-            const float e = fast_exp2(fmaf(s[64 * b + i + w], p.scale_log2, -base));    // exp2(-inf) = 0 for masked keys
+            const float e = fast_exp2(fmaf(s[64 * b + i + w], sc, -base));    // exp2(-inf) = 0 for masked keys
             s[64 * b + i + w] = e;
             s4[w] += e;
           }
@@ -411,6 +433,20 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
         tmem_ld_32x32_issue(to + c * 64 + 32, v + 32);
         tmem_ld_wait();
         if (valid) {
+          if (EXT && x.gate) {                               // the output gate: sigmoid of this row's and head's gate sums
+            const bf16* gr = x.gate + (size_t)(item.row0 + tok) * x.gate_stride + (size_t)(g * p.G + hh) * p.hs + c * 64;
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+              const uint4 gz = *reinterpret_cast<const uint4*>(gr + q8 * 8);
+              const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gz);
+#pragma unroll
+              for (int e2 = 0; e2 < 4; ++e2) {
+                const float2 z = __bfloat1622float2(g2[e2]);
+                v[8 * q8 + 2 * e2] *= 1.f / (1.f + __expf(-z.x));
+                v[8 * q8 + 2 * e2 + 1] *= 1.f / (1.f + __expf(-z.y));
+              }
+            }
+          }
 #pragma unroll
           for (int q8 = 0; q8 < 8; ++q8) {
             uint4 raw;
@@ -441,29 +477,36 @@ SI_EXPORT int si_attn_portion_tc05_ok(int H, int KV, int hs, int page_size) {
 // Tokens of one item: two query tiles of floor(128 / G) each.
 SI_EXPORT int si_attn_portion_tc05_tokens(int H, int KV) { return 2 * (128 / (H / KV)); }
 
-template <int NH>
+template <int NH, bool EXT>
 static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap& vm, int num_items, int log2_page,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const AttnExtras& x) {
   constexpr int HS = NH * 64;
   // Q of both query tiles, two stages of K and of V. The block takes all of tensor memory, so a second
   // block on the same SM could only wait for it: ask for more than half of the shared memory.
   size_t smem = (size_t)(2 * 128 * HS + 2 * 2 * NH * 128 * 64) * sizeof(bf16) + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
-  auto k = attn_portion_tc05_kernel<NH>;
+  auto k = attn_portion_tc05_kernel<NH, EXT>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  si_launch(k, dim3(p.KV, num_items), dim3(320), smem, stream, p, km, vm, log2_page);
+  si_launch(k, dim3(p.KV, num_items), dim3(320), smem, stream, p, km, vm, log2_page, x);
   return si_last_error();
 }
 
 // Same contract as si_attn_portion (attention_mma.cu) with the tensor maps of the layer's K and V cache
 // (made by si_attn_encode_cache_map of attention_tma.cu); items hold at most si_attn_portion_tc05_tokens().
+// `slopes`, the query temperature and `gate` (see AttnExtras) select the extended kernel; without them the plain one runs.
+// Values that are the keys: pass the key cache and its map as the values too.
 SI_EXPORT int si_attn_portion_tc05(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                    const void* kmap, const void* vmap, const int* block_table, int table_width,
                                    const void* items, int num_items, void* out, long long out_stride, int num_pages,
                                    int page_size, int num_seqs, int H, int KV, int hs, float scale, int window,
+                                   const float* slopes, float qt_coef, int qt_every, const void* gate, long long gate_stride,
                                    int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
+  if (qt_every < 0 || (gate && (gate_stride % 8 || ((uintptr_t)gate % 16)))) return -2;
+  // a temperature below zero would turn the order of the scores round: the plain kernels serve that
+  const AttnExtras x{slopes, qt_coef, qt_every, (const bf16*)gate, gate_stride};
+  const bool ext = slopes || qt_every > 0 || gate;
   if (num_items > 65535) return -2;                  // the grid's second dimension
   if (!si_attn_portion_tc05_ok(H, KV, hs, page_size) || !kmap || !vmap) return -2;
   if ((q_stride % 8) || (out_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)out % 16)) return -2;
@@ -482,5 +525,6 @@ SI_EXPORT int si_attn_portion_tc05(const void* q, long long q_stride, const void
   while ((1 << log2_page) < page_size) ++log2_page;
   const CUtensorMap& km = *(const CUtensorMap*)kmap;
   const CUtensorMap& vm = *(const CUtensorMap*)vmap;
-  return hs == 64 ? launch<1>(p, km, vm, num_items, log2_page, stream) : launch<2>(p, km, vm, num_items, log2_page, stream);
+  if (ext) return hs == 64 ? launch<1, true>(p, km, vm, num_items, log2_page, stream, x) : launch<2, true>(p, km, vm, num_items, log2_page, stream, x);
+  return hs == 64 ? launch<1, false>(p, km, vm, num_items, log2_page, stream, x) : launch<2, false>(p, km, vm, num_items, log2_page, stream, x);
 }

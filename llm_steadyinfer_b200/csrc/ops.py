@@ -898,16 +898,27 @@ def attn_portion_tc05_tokens(H: int, KV: int) -> int:
 
 
 def attn_portion_tc05(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int,
-                      KV: int, hs: int, scale: float, window: int = 0, status=None) -> None:
+                      KV: int, hs: int, scale: float, window: int = 0, status=None, slopes=None, q_temp=None, gate=None) -> None:
     """``attn_portion`` on the tcgen05 tensor cores (TMA-fed K/V tiles, S and P V in tensor memory);
-    head_dim 64 or 128, page sizes 8 to 64, items of at most ``attn_portion_tc05_tokens`` tokens."""
+    head_dim 64 or 128, page sizes 8 to 64, items of at most ``attn_portion_tc05_tokens`` tokens. ``v_cache`` None: the
+    values are the keys. ``slopes``, ``q_temp`` (a coefficient that is not negative) and ``gate`` as in ``attention_general``
+    (the gate's rows 16-byte aligned)."""
+    if v_cache is None:
+        v_cache = k_cache
     _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, "attn_portion_tc05")
+    _cuda(slopes, gate)
+    _f32v(slopes, "slopes", H)
+    qt_coef, qt_every = _q_temp(q_temp)
+    _need(qt_coef >= 0.0, "attn_portion_tc05: a query temperature with a negative coefficient is not supported")
+    _need(gate is None or (gate.dtype == torch.bfloat16 and gate.shape == (q.shape[0], H * hs) and gate.stride(1) == 1
+                           and gate.stride(0) % 8 == 0 and gate.data_ptr() % 16 == 0), "attn_portion_tc05: gate must be bf16 [T, H*hs], rows 16-byte aligned")
     f = _fn("attention_tc05", "si_attn_portion_tc05",
             [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p])
+             _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_f, _c_int, _c_p, _c_ll, _c_p, _c_p])
     _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _cache_map(k_cache), _cache_map(v_cache),
              _ptr(block_table), block_table.shape[1], _ptr(items), items.shape[0], _ptr(out), out.stride(0),
-             k_cache.shape[0], page_size, num_seqs, H, KV, hs, float(scale), int(window or 0), _ptr(status),
+             k_cache.shape[0], page_size, num_seqs, H, KV, hs, float(scale), int(window or 0), _ptr(slopes), qt_coef, qt_every,
+             _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(status),
              _stream()), f"attn_portion_tc05(heads={H}, kv_heads={KV}, head_dim={hs}, page_size={page_size})")
 
 

@@ -26,7 +26,9 @@ Options beyond the reference's block, all parameters of the part:
                    ``sigmoid(W_g x)`` before the output projection; its rows are stacked behind q, k, v in one product, and the
                    attention kernels apply the gate when they store their results.
 With any option but ``names`` the mixer runs the general attention kernels (``attention_general.cu`` in 32-bit,
-``attention_flex.cu`` on the tensor cores in bfloat16) instead of the rotary ones.
+``attention_flex.cu`` on the tensor cores in bfloat16) instead of the rotary ones. Sequences that bring a full work item of
+rows to a bfloat16 step go to the tcgen05 prompt kernel (``attention_tc05.cu``) where its layout fits (key size 64 or 128,
+values of the same size or the keys themselves, no bias table): it takes slopes, temperature and gate as well.
 """
 from __future__ import annotations
 
@@ -147,7 +149,7 @@ class Attention(Mixer):
 
     def kernel_files(self, page_size):
         if self.general:
-            return ("attention_general",) + (
+            return ("attention_general",) + (("attention_tc05", "attention_tma") if self.dtype == torch.bfloat16 and self.general_tc05_ok(page_size) else ()) + (
                 ("gemm_f32",) if self.dtype == torch.float32 else ("attention_flex", "gemm_skinny", "gemm_rows", "gemm_tc05"))
         names = ["rope_kv"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_skinny", "gemm_rows", "gemm_tc05"])
         if not self.uses_tensor_cores():
@@ -192,6 +194,37 @@ class Attention(Mixer):
         linear(attn, self.o, out, ctx.status)
         return out
 
+    def general_tc05_ok(self, page_size: int) -> bool:
+        """The general form's long portions on the tcgen05 prompt kernel: its layouts, and nothing it does not know."""
+        return (USE_TC05 and self.bias_spec is None and self.vs == self.hs and (self.q_temp is None or self.q_temp[0] >= 0)
+                and ops.attn_portion_tc05_ok(self.H, self.KV, self.hs, page_size))
+
+    def _plan_general_tc05(self, ctx, page_size: int) -> dict:
+        """Which sequences of the step go to the tcgen05 prompt kernel (those that bring at least one full item of rows),
+        and their work items; the others are the general tensor-core kernel's."""
+        key = ("attention_general_tc05", self.H, self.KV, self.hs, self.window)
+        got = ctx.plans.get(key)
+        if got is not None:
+            return got
+        out = {"skip": frozenset(), "all": False, "items": None}
+        if ctx.seq_cap is None and self.general_tc05_ok(page_size):
+            per = ops.attn_portion_tc05_tokens(self.H, self.KV)
+            qs, cl = ctx.h_q_start, ctx.h_ctx_len
+            chosen, items = [], []
+            for s in range(ctx.num_seqs):
+                row0, n = int(qs[s]), int(qs[s + 1] - qs[s])
+                if n < per:
+                    continue
+                chosen.append(s)
+                pos0 = int(cl[s]) - n
+                items += [(s, row0 + b, min(per, n - b), pos0 + b) for b in range(0, n, per)]
+            if chosen:
+                out = {"skip": frozenset(chosen), "all": len(chosen) == ctx.num_seqs,
+                       "items": ctx.upload_ints(f"attn_gen_tc05_{self.H}_{self.KV}_{self.hs}_{self.window}",
+                                                np.asarray(items, dtype=np.int32)).view(-1, 4)}
+        ctx.plans[key] = out
+        return out
+
     def forward_general(self, x, ctx, cache):
         """No rotation; keys (and values of their own size, where the layer has them) into the pages as they are; scores with
         the bias, the slopes and the query temperature; the gate on the heads' results."""
@@ -206,10 +239,16 @@ class Attention(Mixer):
         attn = ctx.buf("attn_out", (T, H * vs), self.dtype)
         gate = qkv[:, self.gate_off:self.gate_off + H * vs] if self.gate_name else None      # applied in the attention's epilogue
         if self.uses_flex():
-            flex_plan.attend(flex_plan.plan(ctx, self.device, H, KV, hs, vs, self.own_v, self.window), qkv[:, :H * hs], cache.k,
-                             v_cache, cache.block_table, attn, cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale,
-                             self.window, dist_bias=self.dist_bias, status=ctx.status, slopes=self.slopes, q_temp=self.q_temp,
-                             gate=gate)
+            big = self._plan_general_tc05(ctx, cache.page_size)
+            if not big["all"]:
+                flex_plan.attend(flex_plan.plan(ctx, self.device, H, KV, hs, vs, self.own_v, self.window, skip=big["skip"]),
+                                 qkv[:, :H * hs], cache.k, v_cache, cache.block_table, attn, cache.page_size, ctx.seq_slots, H, KV,
+                                 hs, vs, self.scale, self.window, dist_bias=self.dist_bias, status=ctx.status, slopes=self.slopes,
+                                 q_temp=self.q_temp, gate=gate)
+            if big["items"] is not None:
+                ops.attn_portion_tc05(qkv[:, :H * hs], cache.k, v_cache, cache.block_table, big["items"], attn, cache.page_size,
+                                      ctx.seq_slots, H, KV, hs, self.scale, self.window or 0, status=ctx.status,
+                                      slopes=self.slopes, q_temp=self.q_temp, gate=gate)
         else:
             ops.attention_general(qkv[:, :H * hs], cache.k, v_cache, cache.block_table, ctx.row_seq, ctx.positions, attn,
                                   cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale, self.window or 0,
@@ -237,7 +276,9 @@ class Attention(Mixer):
         kernel's item size. One plan serves every layer with the same head layout and window."""
         if self.general:
             if self.uses_flex() and cache.k is not None:
-                flex_plan.plan(ctx, self.device, self.H, self.KV, self.hs, self.vs, self.own_v, self.window)
+                big = self._plan_general_tc05(ctx, cache.page_size)
+                if not big["all"]:
+                    flex_plan.plan(ctx, self.device, self.H, self.KV, self.hs, self.vs, self.own_v, self.window, skip=big["skip"])
             return
         if not self.uses_tensor_cores():
             return

@@ -92,7 +92,7 @@ MIXED_A = model(331, 96, 1e-5, [
 MIXED_B = model(500, 256, 2e-6, [
     layer(latent(8, 32, 16, 40, 80, window=72, base=250.0, scaling={"factor": 8.0, "original": 32, "fast": 4.0, "slow": 2.0}),
           moe(128, 8, 3, 2, limit=1.3, shared=128, shared_limit=1.8)),
-    layer(attn(8, 4, 32, window=33, coef=0.45, every=32), dense(384)),
+    layer(attn(4, 2, 64, window=33, coef=0.45, every=32), dense(384)),
     layer(latent(4, 64, 32, 32, 96, window=40, q_rank=48, with_rank=False), moe(64, 16, 2, 4, limit=1.0, shared=192)),
     layer(attn(16, 4, 16, window=130, coef=0.25, every=50), moe(256, 4, 4, 8, limit=1.2)),
 ], embed_scale=3.5)

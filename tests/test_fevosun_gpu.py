@@ -296,11 +296,12 @@ def _paged(rows, page_size, perm_seed):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("H,G,dk,dv,window,every", [(4, 2, 24, 24, 37, 16), (8, 2, 48, 48, 100, 96), (3, 1, 10, 6, 64, 7), (6, 6, 16, 8, None, 1),
-                                                        (16, 4, 32, 32, 1, 50)])
+                                                        (16, 4, 32, 32, 1, 50), (4, 2, 64, 64, 50, 16), (8, 2, 128, 128, None, 40), (6, 1, 64, 64, 200, 3)])
 def test_attention_with_slopes_temperature_gate_and_keys_as_values(H, G, dk, dv, window, every, dtype):
     """Queries built so that one key carries nearly all of a head's weight without the slopes: keys at page borders, a key far
     back, the key just inside the window and the one just outside. The values are the keys' first entries. Rows run as a
-    prompt and once more one by one; the tensor-core kernel too where the sizes allow it."""
+    prompt and once more one by one; the tensor-core kernels too where the sizes allow it (mma.sync for all rows and single
+    rows, tcgen05 for the prompt)."""
     from llm_steadyinfer_b200.csrc import ops
     torch.manual_seed(3 + H)
     n, ps = 330, 16
@@ -360,6 +361,15 @@ def test_attention_with_slopes_temperature_gate_and_keys_as_values(H, G, dk, dv,
         ops.attn_flex(qd, kc, None, table, items, out2, ps, 1, H, G, dk, dv, scale, window or 0, gate=gate_d, **extra)
         diff = (out2.double().cpu() - want).abs().max().item()
         assert diff <= limit, f"tensor cores, prompt rows: {diff:.2e}"
+        if dk == dv and ops.attn_portion_tc05_ok(H, G, dk, ps):
+            per = ops.attn_portion_tc05_tokens(H, G)
+            items = torch.tensor([(0, b, min(per, n - b), b) for b in range(0, n, per)], dtype=torch.int32, device=DEV)
+            out3 = torch.zeros(n, H * dv, dtype=dtype, device=DEV)
+            status = torch.zeros(1, dtype=torch.int32, device=DEV)
+            ops.attn_portion_tc05(qd, kc, None, table, items, out3, ps, 1, H, G, dk, scale, window or 0, status=status, gate=gate_d, **extra)
+            assert status.item() == 0
+            diff = (out3.double().cpu() - want).abs().max().item()
+            assert diff <= limit, f"tcgen05, prompt rows: {diff:.2e}"
         for nsplit in (1, 3):                             # single rows, their keys whole and cut into shares
             one2 = torch.zeros(last, H * dv, dtype=dtype, device=DEV)
             for r in range(n - last, n):
