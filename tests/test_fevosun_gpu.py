@@ -206,6 +206,25 @@ def test_prompt_equals_token_by_token_in_32_bit(folders):
         assert e < 2e-5, f"prompt and steps differ by {e:.2e}"
 
 
+def test_a_long_portion_beside_short_ones_and_single_tokens(folders, plains):
+    """One step holds a portion long enough for the prompt kernels of many rows, a short portion and single tokens of
+    requests that are further on: each sequence takes its own kernel and every row its own position, window and temperature."""
+    name = "mixed_b"
+    reqs = requests_of(name, [300, 40, 170, 9], seed=6)
+    t = reqs
+    steps = [
+        {"step": 0, "entries": [{"id": "q0", "tokens": t["q0"][:140], "want": [0, 139]}, {"id": "q1", "tokens": t["q1"][:39], "want": [38]}], "end": []},
+        {"step": 1, "entries": [{"id": "q0", "tokens": t["q0"][140:299], "want": [0, 70, 158]}, {"id": "q1", "tokens": t["q1"][39:], "want": [0]},
+                                {"id": "q2", "tokens": t["q2"][:5], "want": [4]}, {"id": "q3", "tokens": t["q3"][:2], "want": [0, 1]}], "end": ["q1"]},
+        {"step": 2, "entries": [{"id": "q2", "tokens": t["q2"][5:169], "want": list(range(0, 164, 13))}, {"id": "q0", "tokens": t["q0"][299:], "want": [0]},
+                                {"id": "q3", "tokens": t["q3"][2:], "want": [6]}], "end": ["q0", "q3"]},
+        {"step": 3, "entries": [{"id": "q2", "tokens": t["q2"][169:], "want": [0]}], "end": ["q2"]},
+    ]
+    for dtype in DTYPES:
+        rp = replayer(folders[name], name, dtype, 640)
+        check(rp, steps, reqs, plains[name], dtype, "long beside short")
+
+
 def test_batch_equals_alone_and_slots_come_again(folders, plains):
     """Unequal requests in one batch against each alone, with two request slots for five requests: every slot and page is
     used again, and the keys that the request before left there must not show."""
