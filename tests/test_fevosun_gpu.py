@@ -24,7 +24,7 @@ pytestmark = pytest.mark.gpu
 # limit. A row whose router had two choice scores closer than MARGIN at the edge of its choice may choose otherwise in
 # bfloat16, which is no fault: such rows are left out there. What a cut, a batch or a page does wrong shows in 32-bit.
 LIMIT = {torch.float32: 2e-4, torch.bfloat16: 8e-2}
-MARGIN = 0.005
+MARGIN = 0.015
 DTYPES = [torch.float32, torch.bfloat16]
 IDS = ["fp32", "bf16"]
 DEV = "cuda:0"
@@ -315,7 +315,8 @@ def _paged(rows, page_size, perm_seed):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("H,G,dk,dv,window,every", [(4, 2, 24, 24, 37, 16), (8, 2, 48, 48, 100, 96), (3, 1, 10, 6, 64, 7), (6, 6, 16, 8, None, 1),
-                                                        (16, 4, 32, 32, 1, 50), (4, 2, 64, 64, 50, 16), (8, 2, 128, 128, None, 40), (6, 1, 64, 64, 200, 3)])
+                                                        (16, 4, 32, 32, 1, 50), (4, 2, 64, 64, 50, 16), (8, 2, 128, 128, None, 40), (6, 1, 64, 64, 200, 3),
+                                                        (2, 2, 64, 64, 70, 5), (8, 1, 128, 128, 129, 11)])
 def test_attention_with_slopes_temperature_gate_and_keys_as_values(H, G, dk, dv, window, every, dtype):
     """Queries built so that one key carries nearly all of a head's weight without the slopes: keys at page borders, a key far
     back, the key just inside the window and the one just outside. The values are the keys' first entries. Rows run as a
