@@ -108,6 +108,40 @@ CONFIGS = {"odd": ODD, "attn": ONLY_ATTN, "lat1": ONLY_LAT1, "lat2": ONLY_LAT2, 
 PAGE_SIZE = {"odd": 4, "attn": 8, "lat1": 16, "lat2": 4, "dense": 8, "moe": 8, "mixed_a": 8, "mixed_b": 16}
 
 
+def random_config(rng, aligned):
+    """A configuration drawn at random (``rng``: random.Random): two to six layers of any kind in any order, windows from
+    1 to 300, heads, sizes, experts and constants over wide ranges; ``aligned``: sizes in multiples of 8 and key sizes that
+    the tensor-core kernels take, else any."""
+    m8 = (lambda lo, hi: 8 * rng.randint(max(1, lo // 8), hi // 8)) if aligned else (lambda lo, hi: rng.randint(lo, hi))
+    layers = []
+    for _ in range(rng.randint(2, 6)):
+        kind = rng.choice(["attention", "latent", "latent2"])
+        window = rng.choice([1, 2, 5, 16, 17, 31, 48, 64, 100, 300])
+        if kind == "attention":
+            kv = rng.choice([1, 2, 3, 4])
+            mx = attn(kv * rng.choice([1, 2, 3, 4]), kv, (rng.choice([16, 64, 64, 128, 24]) if aligned else rng.randint(4, 72)), window=window,
+                      coef=rng.choice([0.0, 0.3, 1.0]), every=rng.choice([1, 4, 13, 64, 1000]), scale=rng.uniform(0.05, 0.4))
+        else:
+            dr = 8 * rng.randint(1, 4) if aligned else 2 * rng.randint(1, 12)
+            sc = rng.choice([None, {"factor": rng.choice([2.0, 8.0, 32.0]), "original": rng.choice([16, 64, 512]),
+                                    "fast": rng.choice([4.0, 32.0]), "slow": rng.choice([1.0, 2.0])}])
+            mx = latent(rng.randint(1, 8), m8(4, 64), dr, m8(4, 64), m8(8, 96), window=window, base=rng.choice([100.0, 10000.0, 1e6]),
+                        scaling=sc, scale=rng.uniform(0.05, 0.3), q_rank=(m8(8, 64) if kind == "latent2" else None),
+                        with_rank=rng.random() < 0.5)
+        r = rng.random()
+        if r < 0.15:
+            mlp = None
+        elif r < 0.4:
+            mlp = dense(m8(8, 200))
+        else:
+            E = rng.randint(1, 20)
+            I = rng.choice([0, 0, 1, 3, 6])
+            mlp = moe(m8(8, 96), E, I, rng.randint(1, min(E + I, 6)), limit=rng.uniform(0.4, 3.0), shared=rng.choice([None, m8(8, 120)]),
+                      shared_limit=rng.uniform(0.4, 3.0))
+        layers.append(layer(mx, mlp))
+    return model(rng.randint(30, 600), m8(24, 160), rng.choice([1e-6, 1e-5]), layers, embed_scale=rng.uniform(0.5, 4.0))
+
+
 def silence_mixer(t):
     """For the configurations that test a feed-forward alone: the mixer's output projection becomes zero."""
     t["l0.mix.o"][:] = 0.0

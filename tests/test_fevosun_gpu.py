@@ -299,6 +299,33 @@ def test_other_sizes_where_the_usual_ones_coincide(tmp_path, plains):
         check(replayer(folder, "odd", dtype, 64), ru.trace_portions(reqs, sizes=(3, 2, 1, 9)), reqs, plain, dtype, "small sizes")
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Layer orders, head counts, sizes, windows, experts and constants drawn at random (even seeds: sizes that the
+    tensor-core kernels take): every schedule in 32-bit, whole prompts and a mixed batch in bfloat16."""
+    import random
+    rng = random.Random(900 + seed)
+    cfg = fc.random_config(rng, aligned=seed % 2 == 0)
+    fc.PAGE_SIZE["random"] = 16 if seed % 2 == 0 else rng.choice([4, 8, 16])
+    folder = fc.write_folder(str(tmp_path / "m"), cfg, 900 + seed)
+    plain = Plain(folder)
+    lens = [1, 2, rng.randint(3, 40), rng.randint(60, 130), rng.randint(150, 300)]
+    reqs = {f"q{i}": ru.random_tokens(cfg["vocab"], n, 7 * seed + i) for i, n in enumerate(lens)}
+    longest = ru.round64(max(lens))
+    for dtype, modes in ((torch.float32, ("whole", "tail", "portions", "mixed")), (torch.bfloat16, ("whole", "mixed"))):
+        for mode in modes:
+            if mode == "whole":
+                steps, mt = ru.trace_whole(reqs), longest
+            elif mode == "tail":
+                steps, mt = ru.trace_tail(reqs, tail=40), longest
+            elif mode == "portions":
+                steps, mt = ru.trace_portions(reqs, sizes=(2, 17, 3, 2, 31, 5, 64, 2, 9, 1, 40, 100)), longest
+            else:
+                mt = longest + 128
+                steps = ru.trace_mixed(reqs, mt, seed=seed, max_live=4)
+            check(replayer(folder, "random", dtype, mt, max_requests=4), steps, reqs, plain, dtype, f"random {seed}/{mode}")
+
+
 # ---- kernels ----------------------------------------------------------------------------------------------
 
 def _paged(rows, page_size, perm_seed):
